@@ -1,0 +1,201 @@
+// Device layer of the C ABI: argument checks and kernel dispatch.  Nothing here allocates,
+// synchronises or exits; every pointer is a device pointer on the current device.
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "common.cuh"
+
+#define GRPO_STR2(x) #x
+#define GRPO_STR(x) GRPO_STR2(x)
+
+namespace grpo_b200 {
+
+namespace {
+thread_local std::string g_error;
+}
+
+void set_error(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_error = buf;
+}
+
+int cuda_fail(cudaError_t err, const char* what) {
+    set_error("CUDA error: %s (%s)", cudaGetErrorString(err), what);
+    return GRPO_B200_E_CUDA;
+}
+
+namespace {
+
+int invalid(const char* msg) {
+    set_error("%s", msg);
+    return GRPO_B200_E_INVALID;
+}
+
+// Option ranges, with the reference's messages (src/cuda/grpo_loss_cuda.cu:596-601).
+int check_options(float clip_eps, float beta) {
+    if (!(clip_eps >= 0.0f && clip_eps < 1.0f)) return invalid("clip_eps must be finite and in [0, 1)");
+    if (!(beta >= 0.0f && beta <= 3.402823466e+38f)) return invalid("beta must be finite and non-negative");
+    return GRPO_B200_OK;
+}
+
+constexpr long long kIntMax = 2147483647LL;
+
+}  // namespace
+}  // namespace grpo_b200
+
+using namespace grpo_b200;
+
+extern "C" {
+
+const char* grpo_b200_last_error(void) { return g_error.c_str(); }
+
+const char* grpo_b200_build_info(void) { return "grpo_b200 0.1 (sm_100a, CUDA " GRPO_STR(CUDART_VERSION) ")"; }
+
+int grpo_b200_count_lengths(const int32_t* mask, int64_t n_rows, int64_t row_offset, int tokens_per_seq,
+                            int64_t n_seq, int32_t* lengths, grpo_b200_stream_t stream) {
+    if (!mask || !lengths) return invalid("mask and lengths must not be null");
+    if (n_rows <= 0 || n_seq <= 0 || tokens_per_seq <= 0 || row_offset < 0)
+        return invalid("B, G and T must be positive");
+    if (n_seq > kIntMax) return invalid("sequence count exceeds INT_MAX");
+    if (row_offset + n_rows > n_seq * static_cast<int64_t>(tokens_per_seq))
+        return invalid("local rows reach past the end of the batch");
+    GRPO_CUDA_TRY(launch_count_lengths(mask, n_rows, row_offset, tokens_per_seq, n_seq, lengths,
+                                       reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_weights_from_lengths(const int32_t* lengths, int64_t n_seq, int reduction, float length_alpha,
+                                   float* weights, int32_t* meta, grpo_b200_stream_t stream) {
+    if (!lengths || !weights || !meta) return invalid("lengths, weights and meta must not be null");
+    if (n_seq <= 0) return invalid("B, G and T must be positive");
+    if (n_seq > kIntMax) return invalid("sequence count exceeds INT_MAX");
+    if (reduction < 0 || reduction > 2) return invalid("unknown reduction mode");
+    if (!(length_alpha >= 0.0f && length_alpha <= 1.0f)) return invalid("length_alpha must be finite and in [0, 1]");
+    GRPO_CUDA_TRY(launch_weights(lengths, n_seq, reduction, length_alpha, weights, meta,
+                                 reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_group_advantages(const float* rewards, int B, int G, int mode, float eps, float* advantages,
+                               int32_t* meta, grpo_b200_stream_t stream) {
+    if (!rewards || !advantages || !meta) return invalid("rewards, advantages and meta must not be null");
+    if (B <= 0 || G <= 0) return invalid("B, G and T must be positive");
+    if (static_cast<long long>(B) * G > kIntMax) return invalid("sequence count exceeds INT_MAX");
+    if (!(eps >= 0.0f && eps <= 3.402823466e+38f)) return invalid("eps must be finite and non-negative");
+    if (mode != GRPO_B200_ADV_STANDARDIZED && mode != GRPO_B200_ADV_CENTERED) return invalid("unknown advantage mode");
+    GRPO_CUDA_TRY(launch_group_advantages(rewards, B, G, mode, eps, advantages, meta,
+                                          reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
+size_t grpo_b200_loss_workspace_bytes(int64_t n_tokens) {
+    (void)n_tokens;
+    return static_cast<size_t>(2048) * 5 * sizeof(double);  // per-block partials, fixed upper bound
+}
+
+int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* logp_ref, const float* advantages,
+                   const float* weights, const int32_t* mask, int64_t n_tokens, int64_t token_offset,
+                   int tokens_per_seq, float clip_eps, float beta, float* dlogp, grpo_b200_result_t* result,
+                   void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream) {
+    if (!logp_new || !logp_old || !logp_ref || !advantages || !weights || !mask || !dlogp || !result)
+        return invalid("device pointers must not be null");
+    if (n_tokens <= 0 || tokens_per_seq <= 0 || token_offset < 0) return invalid("B, G and T must be positive");
+    if (token_offset + n_tokens > kIntMax) return invalid("token count exceeds INT_MAX");
+    if (int rc = check_options(clip_eps, beta)) return rc;
+    if (!workspace || workspace_bytes < grpo_b200_loss_workspace_bytes(n_tokens) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 7u)) {
+        set_error("workspace must be 8-byte aligned and hold grpo_b200_loss_workspace_bytes() bytes");
+        return GRPO_B200_E_WORKSPACE;
+    }
+    LossArgs a;
+    a.logp_new = logp_new;
+    a.logp_old = logp_old;
+    a.logp_ref = logp_ref;
+    a.advantages = advantages;
+    a.weights = weights;
+    a.mask = mask;
+    a.n_tokens = n_tokens;
+    a.token_offset = token_offset;
+    a.tokens_per_seq = tokens_per_seq;
+    a.clip_eps = clip_eps;
+    a.beta = beta;
+    a.dlogp = dlogp;
+    a.result = result;
+    a.partials = static_cast<double*>(workspace);
+    GRPO_CUDA_TRY(launch_loss(a, reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
+size_t grpo_b200_logits_workspace_bytes(int64_t n_rows) {
+    return n_rows > 0 ? static_cast<size_t>(n_rows) * sizeof(float4) : 0;  // per-row loss terms
+}
+
+int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
+                     const int32_t* selected, const float* advantages, const float* weights, const int32_t* mask,
+                     int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P, float clip_eps,
+                     float beta, int kernel, int check_inputs, float* selected_logp, grpo_b200_result_t* result,
+                     void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream) {
+    if (!logits || !dlogits) return invalid("logits_and_dlogits must not be null");
+    if (!logp_old || !logp_ref || !selected || !advantages || !weights || !mask || !result)
+        return invalid("device pointers must not be null");
+    if (n_rows <= 0 || tokens_per_seq <= 0 || row_offset < 0) return invalid("B, G and T must be positive");
+    if (row_offset + n_rows > kIntMax) return invalid("token count exceeds INT_MAX");
+    if (V <= 0) return invalid("V must be positive");
+    if (P < V) return invalid("P must be at least V");
+    if (kernel != GRPO_B200_LOGITS_SEPARATE && kernel != GRPO_B200_LOGITS_FUSED)
+        return invalid("unknown logits kernel selector");
+    if (int rc = check_options(clip_eps, beta)) return rc;
+    if (!workspace || workspace_bytes < grpo_b200_logits_workspace_bytes(n_rows) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
+        set_error("workspace must be 16-byte aligned and hold grpo_b200_logits_workspace_bytes() bytes");
+        return GRPO_B200_E_WORKSPACE;
+    }
+    LogitsArgs a;
+    a.logits = logits;
+    a.dlogits = dlogits;
+    a.logp_old = logp_old;
+    a.logp_ref = logp_ref;
+    a.selected = selected;
+    a.advantages = advantages;
+    a.weights = weights;
+    a.mask = mask;
+    a.n_rows = n_rows;
+    a.row_offset = row_offset;
+    a.tokens_per_seq = tokens_per_seq;
+    a.V = V;
+    a.P = P;
+    a.clip_eps = clip_eps;
+    a.beta = beta;
+    a.row_terms = static_cast<float4*>(workspace);
+    a.selected_logp = selected_logp;
+    a.result = result;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int variant = kernel == GRPO_B200_LOGITS_FUSED ? pick_resident_variant(logits, dlogits, V, P) : -1;
+    if (variant >= 0)
+        GRPO_CUDA_TRY(launch_logits_resident(variant, check_inputs != 0, a, s));
+    else
+        GRPO_CUDA_TRY(launch_logits_streaming(check_inputs != 0, a, s));
+    GRPO_CUDA_TRY(launch_logits_finalize(a, s));
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_logits_set_variant(int variant) {
+    if (variant >= resident_variant_count()) return invalid("no such kernel variant");
+    g_forced_variant = variant < 0 ? -1 : variant;
+    return GRPO_B200_OK;
+}
+
+const char* grpo_b200_logits_variant_name(int variant) { return resident_variant_name(variant); }
+
+const char* grpo_b200_logits_plan(const void* logits, const void* dlogits, int V, int P, int kernel) {
+    if (kernel != GRPO_B200_LOGITS_FUSED) return "streaming";
+    const int v = pick_resident_variant(logits, dlogits, V, P);
+    return v >= 0 ? resident_variant_name(v) : "streaming";
+}
+
+}  // extern "C"

@@ -1,0 +1,167 @@
+// Shared device helpers of the GRPO loss-boundary kernels (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "grpo_b200.h"
+
+namespace grpo_b200 {
+
+// ---- error text (thread-local, read back through grpo_b200_last_error) ---------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t err, const char* what);
+
+#define GRPO_CUDA_TRY(expr)                                             \
+    do {                                                                \
+        cudaError_t err__ = (expr);                                     \
+        if (err__ != cudaSuccess) return ::grpo_b200::cuda_fail(err__, #expr); \
+    } while (0)
+
+// ---- per-token loss ------------------------------------------------------------------------
+// The four weighted terms of one active token.  Arithmetic mirrors the reference's CPU path
+// (src/cpu/grpo_loss.cpp:137-160; its CUDA twin token_loss, src/cuda/grpo_loss_cuda.cu:59-95)
+// one fp32 operation at a time: explicit round-to-nearest intrinsics keep the compiler from
+// fusing a multiply into an add, because the CPU build has no fused multiply-add.
+struct TokenTerms {
+    float loss, pg, kl, grad;
+};
+
+// PRECISE = true evaluates exp / expm1 in double and rounds to fp32 (matches a correctly
+// rounded libm expf in all but the rarest cases; used where there is one token per row of
+// logits).  PRECISE = false uses the fp32 device functions (<= 2 ulp), for the path that runs
+// millions of tokens per launch.
+template <bool PRECISE>
+__device__ __forceinline__ TokenTerms token_terms(float lp_new, float lp_old, float lp_ref,
+                                                  float adv, float w, float clip_eps, float beta) {
+    const float lo = __fsub_rn(1.0f, clip_eps);
+    const float hi = __fadd_rn(1.0f, clip_eps);
+    float pg = 0.0f, pg_grad = 0.0f;
+    if (adv != 0.0f) {  // a zero advantage never evaluates the ratio (overflow-safe)
+        const float a = __fsub_rn(lp_new, lp_old);
+        const float rho = PRECISE ? static_cast<float>(exp(static_cast<double>(a))) : expf(a);
+        const float rho_c = rho < lo ? lo : (hi < rho ? hi : rho);
+        const float u = __fmul_rn(rho, adv);
+        const float c = __fmul_rn(rho_c, adv);
+        pg = -(c < u ? c : u);
+        // strictly outside the window on the side the advantage pushes towards: no gradient;
+        // exactly on the boundary the unclipped branch is kept
+        const bool cut = (adv > 0.0f && rho > hi) || (adv < 0.0f && rho < lo);
+        pg_grad = cut ? 0.0f : __fmul_rn(-adv, rho);
+    }
+    const float d = __fsub_rn(lp_ref, lp_new);
+    const float em1 = PRECISE ? static_cast<float>(expm1(static_cast<double>(d))) : expm1f(d);
+    const float kl = __fsub_rn(em1, d);  // k3 estimator: e^d - 1 - d >= 0
+    const float loss = __fadd_rn(pg, __fmul_rn(beta, kl));
+    const float kl_grad = __fmul_rn(-beta, em1);
+    TokenTerms t;
+    t.loss = __fmul_rn(w, loss);
+    t.pg = __fmul_rn(w, pg);
+    t.kl = __fmul_rn(w, kl);
+    t.grad = __fmul_rn(w, __fadd_rn(pg_grad, kl_grad));
+    return t;
+}
+
+__device__ __forceinline__ bool finite_f(float x) { return fabsf(x) <= 3.402823466e+38f; }
+
+// ---- deterministic reductions ----------------------------------------------------------------
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    return v;  // lane 0 holds the sum; the tree shape is fixed
+}
+
+// Sums NV doubles per thread over a block of THREADS threads (fixed tree: lanes, then warps in
+// index order).  Thread 0 returns the totals in v[]; `scratch` needs NV * THREADS/32 doubles.
+template <int THREADS, int NV>
+__device__ __forceinline__ void block_sum(double (&v)[NV], double* scratch) {
+    constexpr int WARPS = THREADS / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        v[k] = warp_sum(v[k]);
+        if (lane == 0) scratch[k * WARPS + warp] = v[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            double x = lane < WARPS ? scratch[k * WARPS + lane] : 0.0;
+            v[k] = warp_sum(x);
+        }
+    }
+}
+
+// base-2 exponential on the special-function unit (max relative error about 2^-22)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr double kLn2 = 0.693147180559945309417232121458;
+
+// streaming (evict-first) 128-bit accesses: every logit is touched exactly once
+__device__ __forceinline__ float4 load_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void store_stream(float4* p, float4 v) { __stcs(p, v); }
+
+// ---- kernel launchers (device layer back end) -------------------------------------------------
+struct LossArgs {
+    const float* logp_new;
+    const float* logp_old;
+    const float* logp_ref;
+    const float* advantages;
+    const float* weights;
+    const int32_t* mask;
+    long long n_tokens;
+    long long token_offset;
+    int tokens_per_seq;
+    float clip_eps, beta;
+    float* dlogp;
+    grpo_b200_result_t* result;
+    double* partials;  // [blocks][4]
+};
+int loss_grid_blocks(long long n_tokens);
+cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream);
+
+struct LogitsArgs {
+    const float* logits;
+    float* dlogits;
+    const float* logp_old;
+    const float* logp_ref;
+    const int32_t* selected;
+    const float* advantages;
+    const float* weights;
+    const int32_t* mask;
+    long long n_rows;
+    long long row_offset;
+    int tokens_per_seq;
+    int V, P;
+    float clip_eps, beta;
+    float4* row_terms;  // [n_rows] {w*loss, w*pg, w*kl, flags}
+    float* selected_logp;
+    grpo_b200_result_t* result;
+};
+// flags stored in row_terms.w (small integers, exact in fp32)
+constexpr float kRowBadGrad = 1.0f;
+constexpr float kRowBadInput = 2.0f;
+
+int pick_resident_variant(const void* logits, const void* dlogits, int V, int P);
+const char* resident_variant_name(int variant);
+int resident_variant_count();
+extern int g_forced_variant;
+cudaError_t launch_logits_resident(int variant, bool check, const LogitsArgs& a, cudaStream_t stream);
+cudaError_t launch_logits_streaming(bool check, const LogitsArgs& a, cudaStream_t stream);
+cudaError_t launch_logits_finalize(const LogitsArgs& a, cudaStream_t stream);
+
+cudaError_t launch_count_lengths(const int32_t* mask, long long n_rows, long long row_offset,
+                                 int tokens_per_seq, long long n_seq, int32_t* lengths,
+                                 cudaStream_t stream);
+cudaError_t launch_weights(const int32_t* lengths, long long n_seq, int reduction, float alpha,
+                           float* weights, int32_t* meta, cudaStream_t stream);
+cudaError_t launch_group_advantages(const float* rewards, int B, int G, int mode, float eps,
+                                    float* advantages, int32_t* meta, cudaStream_t stream);
+
+}  // namespace grpo_b200

@@ -1,0 +1,278 @@
+// Selected-token GRPO loss (K1), valid-token counting, response weights and group advantages.
+//
+// K1 replaces the reference's grpo_loss_block_kernel / grpo_loss_atomic_kernel
+// (src/cuda/grpo_loss_cuda.cu:97-179).  Differences by design:
+//   * 128-bit loads: one thread owns four consecutive tokens per step, so the three
+//     log-probability streams, the mask and dlogp move as float4/int4 (20 B per active token,
+//     8 B per fully masked group of the input streams is never fetched);
+//   * the three sums are carried in double from fp32 per-token products -- the same recipe as
+//     the CPU path (src/cpu/grpo_loss.cpp:114-116,157-159) -- through a fixed shuffle tree, a
+//     fixed warp-order tree per block and a fixed-order pass over per-block partials: no
+//     global atomics, bit-identical results from run to run;
+//   * no accumulator memset: the finalize step overwrites the result record.
+#include "common.cuh"
+
+namespace grpo_b200 {
+
+namespace {
+
+constexpr int kLossThreads = 256;
+constexpr int kLossMaxBlocks = 2048;  // bounds the per-block partials the finalize pass reads
+constexpr int kPartialWidth = 5;      // loss, pg, kl, bad gradients, bad inputs
+
+struct Acc {
+    double v[kPartialWidth];
+};
+
+__device__ __forceinline__ float one_token(const LossArgs& a, float lp_new, float lp_old, float lp_ref,
+                                           int m, long long seq, Acc& acc) {
+    if (m == 0) return 0.0f;
+    const float adv = __ldg(a.advantages + seq);
+    const float w = __ldg(a.weights + seq);
+    const TokenTerms t = token_terms<false>(lp_new, lp_old, lp_ref, adv, w, a.clip_eps, a.beta);
+    acc.v[0] += static_cast<double>(t.loss);
+    acc.v[1] += static_cast<double>(t.pg);
+    acc.v[2] += static_cast<double>(t.kl);
+    if (!finite_f(t.grad)) acc.v[3] += 1.0;
+    if (m != 1 || !finite_f(lp_new) || !finite_f(lp_old) || !finite_f(lp_ref)) acc.v[4] += 1.0;
+    return t.grad;
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kLossThreads) token_loss_kernel(const LossArgs a) {
+    __shared__ double scratch[kPartialWidth * kLossThreads / 32];
+    Acc acc;
+#pragma unroll
+    for (int k = 0; k < kPartialWidth; k++) acc.v[k] = 0.0;
+
+    const long long tid = static_cast<long long>(blockIdx.x) * kLossThreads + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * kLossThreads;
+    const long long T = a.tokens_per_seq;
+
+    if (VEC) {
+        const long long groups = a.n_tokens >> 2;
+        for (long long g = tid; g < groups; g += stride) {
+            const int4 m = __ldg(reinterpret_cast<const int4*>(a.mask) + g);
+            float4 grad = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if ((m.x | m.y | m.z | m.w) != 0) {
+                const float4 ln = __ldcs(reinterpret_cast<const float4*>(a.logp_new) + g);
+                const float4 lo = __ldcs(reinterpret_cast<const float4*>(a.logp_old) + g);
+                const float4 lr = __ldcs(reinterpret_cast<const float4*>(a.logp_ref) + g);
+                const long long i0 = a.token_offset + 4 * g;
+                long long seq = i0 / T;
+                long long rem = i0 - seq * T;
+                grad.x = one_token(a, ln.x, lo.x, lr.x, m.x, seq, acc);
+                if (++rem == T) { rem = 0; ++seq; }
+                grad.y = one_token(a, ln.y, lo.y, lr.y, m.y, seq, acc);
+                if (++rem == T) { rem = 0; ++seq; }
+                grad.z = one_token(a, ln.z, lo.z, lr.z, m.z, seq, acc);
+                if (++rem == T) { rem = 0; ++seq; }
+                grad.w = one_token(a, ln.w, lo.w, lr.w, m.w, seq, acc);
+            }
+            __stcs(reinterpret_cast<float4*>(a.dlogp) + g, grad);
+        }
+        // the up-to-three tokens past the last full group
+        const long long i = (groups << 2) + tid;
+        if (i < a.n_tokens) {
+            const int m = a.mask[i];
+            float g1 = 0.0f;
+            if (m != 0)
+                g1 = one_token(a, a.logp_new[i], a.logp_old[i], a.logp_ref[i], m,
+                               (a.token_offset + i) / T, acc);
+            a.dlogp[i] = g1;
+        }
+    } else {
+        for (long long i = tid; i < a.n_tokens; i += stride) {
+            const int m = a.mask[i];
+            float g1 = 0.0f;
+            if (m != 0)
+                g1 = one_token(a, a.logp_new[i], a.logp_old[i], a.logp_ref[i], m,
+                               (a.token_offset + i) / T, acc);
+            a.dlogp[i] = g1;
+        }
+    }
+
+    block_sum<kLossThreads, kPartialWidth>(acc.v, scratch);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int k = 0; k < kPartialWidth; k++) a.partials[blockIdx.x * kPartialWidth + k] = acc.v[k];
+    }
+}
+
+// One block walks the per-block partials in index order and overwrites the result record.
+__global__ void __launch_bounds__(256) loss_finalize_kernel(const double* __restrict__ partials, int n,
+                                                            grpo_b200_result_t* result) {
+    __shared__ double scratch[kPartialWidth * 256 / 32];
+    double v[kPartialWidth];
+#pragma unroll
+    for (int k = 0; k < kPartialWidth; k++) v[k] = 0.0;
+    for (int b = threadIdx.x; b < n; b += 256) {
+#pragma unroll
+        for (int k = 0; k < kPartialWidth; k++) v[k] += partials[b * kPartialWidth + k];
+    }
+    block_sum<256, kPartialWidth>(v, scratch);
+    if (threadIdx.x == 0) {
+        result->loss = v[0];
+        result->pg_loss = v[1];
+        result->kl = v[2];
+        result->bad_grads = v[3];
+        result->bad_inputs = v[4];
+    }
+}
+
+// One warp per response: counts the non-zero mask entries of its local token range.
+__global__ void __launch_bounds__(256) count_lengths_kernel(const int32_t* __restrict__ mask, long long n_rows,
+                                                            long long row_offset, long long T, long long n_seq,
+                                                            int32_t* __restrict__ lengths) {
+    const long long seq = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 5;
+    if (seq >= n_seq) return;
+    const int lane = threadIdx.x & 31;
+    long long lo = seq * T, hi = lo + T;
+    if (lo < row_offset) lo = row_offset;
+    if (hi > row_offset + n_rows) hi = row_offset + n_rows;
+    int count = 0;
+    for (long long i = lo + lane; i < hi; i += 32) count += __ldg(mask + (i - row_offset)) != 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) count += __shfl_down_sync(0xffffffffu, count, o);
+    if (lane == 0) lengths[seq] = count;
+}
+
+// Single block: total of the lengths, number of empty responses, then the weights with the
+// reference's fp32 expressions (src/cuda/grpo_loss_cuda.cu:43-55).  The power is evaluated in
+// double and rounded, which reproduces a correctly rounded powf.
+__global__ void __launch_bounds__(1024) weights_kernel(const int32_t* __restrict__ lengths, long long n_seq,
+                                                       int reduction, float alpha, float* __restrict__ weights,
+                                                       int32_t* __restrict__ meta) {
+    __shared__ double scratch[2 * 1024 / 32];
+    __shared__ double total_sh;
+    double v[2] = {0.0, 0.0};
+    for (long long s = threadIdx.x; s < n_seq; s += 1024) {
+        const int L = lengths[s];
+        v[0] += static_cast<double>(L);
+        v[1] += L == 0 ? 1.0 : 0.0;
+    }
+    block_sum<1024, 2>(v, scratch);
+    if (threadIdx.x == 0) {
+        total_sh = v[0];
+        meta[0] = static_cast<int32_t>(v[0]);
+        meta[1] = static_cast<int32_t>(v[1]);
+    }
+    __syncthreads();
+    const float n_valid = static_cast<float>(static_cast<int32_t>(total_sh));
+    const float n_seq_f = static_cast<float>(n_seq);
+    const float expo = __fsub_rn(alpha, 1.0f);
+    for (long long s = threadIdx.x; s < n_seq; s += 1024) {
+        const int L = lengths[s];
+        float w = 0.0f;
+        if (L > 0) {
+            const float Lf = static_cast<float>(L);
+            if (reduction == GRPO_B200_SEQUENCE_MEAN) {
+                w = __fdiv_rn(1.0f, __fmul_rn(n_seq_f, Lf));
+            } else if (reduction == GRPO_B200_TOKEN_MEAN) {
+                w = __fdiv_rn(1.0f, n_valid);
+            } else {
+                const float p = static_cast<float>(pow(static_cast<double>(Lf), static_cast<double>(expo)));
+                w = __fdiv_rn(p, n_seq_f);
+            }
+        }
+        weights[s] = w;
+    }
+}
+
+// One thread per prompt walks its G rewards in order: Welford mean / M2 in double with
+// unfused IEEE operations, exactly the CPU sequence (src/cpu/grpo_loss.cpp:31-52).
+__global__ void __launch_bounds__(256) group_advantages_kernel(const float* __restrict__ rewards, int B, int G,
+                                                               int mode, float eps, float* __restrict__ adv,
+                                                               int32_t* __restrict__ meta) {
+    __shared__ double scratch[256 / 32];
+    double bad[1] = {0.0};
+    for (int b = threadIdx.x; b < B; b += 256) {
+        const float* r = rewards + static_cast<long long>(b) * G;
+        float* a = adv + static_cast<long long>(b) * G;
+        const float first = r[0];
+        bool same = true;
+        for (int g = 0; g < G; g++) {
+            const float x = r[g];
+            same = same && (x == first);
+            if (!finite_f(x)) bad[0] += 1.0;
+        }
+        if (same) {
+            for (int g = 0; g < G; g++) a[g] = 0.0f;
+            continue;
+        }
+        double mean = 0.0, m2 = 0.0;
+        for (int g = 0; g < G; g++) {
+            const double x = r[g];
+            const double delta = __dsub_rn(x, mean);
+            mean = __dadd_rn(mean, __ddiv_rn(delta, static_cast<double>(g + 1)));
+            m2 = __dadd_rn(m2, __dmul_rn(delta, __dsub_rn(x, mean)));
+        }
+        const double var = __ddiv_rn(m2, static_cast<double>(G));
+        const double denom = mode == GRPO_B200_ADV_STANDARDIZED ? __dsqrt_rn(__dadd_rn(var, static_cast<double>(eps))) : 1.0;
+        for (int g = 0; g < G; g++) {
+            const float out = static_cast<float>(__ddiv_rn(__dsub_rn(static_cast<double>(r[g]), mean), denom));
+            if (!finite_f(out)) bad[0] += 1.0;
+            a[g] = out;
+        }
+    }
+    block_sum<256, 1>(bad, scratch);
+    if (threadIdx.x == 0) meta[0] = static_cast<int32_t>(bad[0]);
+}
+
+int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
+    return sms;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+int loss_grid_blocks(long long n_tokens) {
+    const long long groups = (n_tokens + 3) / 4;
+    long long blocks = (groups + kLossThreads - 1) / kLossThreads;
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks > kLossMaxBlocks) blocks = kLossMaxBlocks;
+    if (blocks < 1) blocks = 1;
+    return static_cast<int>(blocks);
+}
+
+cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream) {
+    const int blocks = loss_grid_blocks(a.n_tokens);
+    const bool vec = aligned16(a.logp_new) && aligned16(a.logp_old) && aligned16(a.logp_ref) &&
+                     aligned16(a.mask) && aligned16(a.dlogp);
+    if (vec)
+        token_loss_kernel<true><<<blocks, kLossThreads, 0, stream>>>(a);
+    else
+        token_loss_kernel<false><<<blocks, kLossThreads, 0, stream>>>(a);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    loss_finalize_kernel<<<1, 256, 0, stream>>>(a.partials, blocks, a.result);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_count_lengths(const int32_t* mask, long long n_rows, long long row_offset, int tokens_per_seq,
+                                 long long n_seq, int32_t* lengths, cudaStream_t stream) {
+    const long long threads = n_seq * 32;
+    const long long blocks = (threads + 255) / 256;
+    count_lengths_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(mask, n_rows, row_offset, tokens_per_seq,
+                                                                            n_seq, lengths);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_weights(const int32_t* lengths, long long n_seq, int reduction, float alpha, float* weights,
+                           int32_t* meta, cudaStream_t stream) {
+    weights_kernel<<<1, 1024, 0, stream>>>(lengths, n_seq, reduction, alpha, weights, meta);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_group_advantages(const float* rewards, int B, int G, int mode, float eps, float* advantages,
+                                    int32_t* meta, cudaStream_t stream) {
+    group_advantages_kernel<<<1, 256, 0, stream>>>(rewards, B, G, mode, eps, advantages, meta);
+    return cudaGetLastError();
+}
+
+}  // namespace grpo_b200

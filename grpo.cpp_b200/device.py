@@ -1,0 +1,180 @@
+"""Device layer of the C ABI on torch CUDA tensors.
+
+torch supplies device memory and the current stream; every computation below is a kernel of
+``libgrpo_b200.so`` enqueued on that stream through the C ABI (``include/grpo_b200.h``).  Nothing
+here synchronises or copies to the host; results stay in a device record of five doubles
+``[loss, pg_loss, kl, bad_grads, bad_inputs]``.
+
+The calls replace, with everything resident on the device, what the reference does per call on
+the host plus its kernels: make_weights (src/cuda/grpo_loss_cuda.cu:21-57), launch_loss (:527-549)
+and launch_logits (:551-582).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .api import CudaLogitsKernel, ReductionMode
+
+RESULT_FIELDS = ("loss", "pg_loss", "kl", "bad_grads", "bad_inputs")
+
+
+def _check_tensor(t: torch.Tensor, dtype, name: str) -> int:
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise TypeError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def new_result(device=None) -> torch.Tensor:
+    return torch.zeros(5, dtype=torch.float64, device=device or torch.cuda.current_device())
+
+
+def count_lengths(mask: torch.Tensor, n_seq: int, tokens_per_seq: int, row_offset: int = 0,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """Valid tokens per response among the local rows ``[row_offset, row_offset + len(mask))``."""
+    m = _check_tensor(mask, torch.int32, "mask")
+    if out is None:
+        out = torch.empty(n_seq, dtype=torch.int32, device=mask.device)
+    o = _check_tensor(out, torch.int32, "lengths")
+    _lib.check(_lib.lib().grpo_b200_count_lengths(m, mask.numel(), row_offset, tokens_per_seq, n_seq, o, _stream()))
+    return out
+
+
+def weights_from_lengths(lengths: torch.Tensor, reduction: int, length_alpha: float = 0.0,
+                         out: torch.Tensor | None = None, meta: torch.Tensor | None = None):
+    """Per-response weights from global lengths; ``meta = [valid_tokens, empty_responses]`` (int32)."""
+    l = _check_tensor(lengths, torch.int32, "lengths")
+    if out is None:
+        out = torch.empty(lengths.numel(), dtype=torch.float32, device=lengths.device)
+    if meta is None:
+        meta = torch.zeros(2, dtype=torch.int32, device=lengths.device)
+    _lib.check(_lib.lib().grpo_b200_weights_from_lengths(
+        l, lengths.numel(), int(reduction), float(length_alpha), _check_tensor(out, torch.float32, "weights"),
+        _check_tensor(meta, torch.int32, "meta"), _stream()))
+    return out, meta
+
+
+def group_advantages(rewards: torch.Tensor, B: int, G: int, mode: int = 0, eps: float = 1e-8):
+    """Group-relative advantages ``[B*G]``; ``meta[0]`` counts non-finite rewards/advantages."""
+    r = _check_tensor(rewards, torch.float32, "rewards")
+    if rewards.numel() != B * G:
+        raise RuntimeError(f"rewards has size {rewards.numel()}, expected {B * G}")
+    out = torch.empty(B * G, dtype=torch.float32, device=rewards.device)
+    meta = torch.zeros(1, dtype=torch.int32, device=rewards.device)
+    _lib.check(_lib.lib().grpo_b200_group_advantages(r, B, G, int(mode), float(eps), out.data_ptr(),
+                                                    meta.data_ptr(), _stream()))
+    return out, meta
+
+
+def loss_workspace(device=None) -> torch.Tensor:
+    n = _lib.lib().grpo_b200_loss_workspace_bytes(1)
+    return torch.empty(n, dtype=torch.uint8, device=device or torch.cuda.current_device())
+
+
+def loss(logp_new, logp_old, logp_ref, advantages, weights, mask, tokens_per_seq: int, clip_eps: float,
+         beta: float, *, token_offset: int = 0, dlogp: torch.Tensor | None = None,
+         result: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+    """Selected-token path on device tensors.  Returns ``(dlogp, result)``."""
+    n = logp_new.numel()
+    if dlogp is None:
+        dlogp = torch.empty(n, dtype=torch.float32, device=logp_new.device)
+    if result is None:
+        result = new_result(logp_new.device)
+    if workspace is None:
+        workspace = loss_workspace(logp_new.device)
+    _lib.check(_lib.lib().grpo_b200_loss(
+        _check_tensor(logp_new, torch.float32, "logp_new"), _check_tensor(logp_old, torch.float32, "logp_old"),
+        _check_tensor(logp_ref, torch.float32, "logp_ref"), _check_tensor(advantages, torch.float32, "advantages"),
+        _check_tensor(weights, torch.float32, "weights"), _check_tensor(mask, torch.int32, "mask"),
+        n, token_offset, tokens_per_seq, float(clip_eps), float(beta),
+        _check_tensor(dlogp, torch.float32, "dlogp"), _check_tensor(result, torch.float64, "result"),
+        workspace.data_ptr(), workspace.numel(), _stream()))
+    return dlogp, result
+
+
+def logits_workspace(n_rows: int, device=None) -> torch.Tensor:
+    n = _lib.lib().grpo_b200_logits_workspace_bytes(n_rows)
+    return torch.empty(n, dtype=torch.uint8, device=device or torch.cuda.current_device())
+
+
+def logits(logits_t: torch.Tensor, logp_old, logp_ref, selected, advantages, weights, mask,
+           tokens_per_seq: int, V: int, clip_eps: float, beta: float, *, dlogits: torch.Tensor | None = None,
+           row_offset: int = 0, kernel: int = CudaLogitsKernel.fused, check_inputs: bool = False,
+           selected_logp: torch.Tensor | None = None, result: torch.Tensor | None = None,
+           workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Logits path on device tensors: ``logits_t`` is ``[n_rows, P]`` fp32; ``dlogits=None`` means in
+    place.  Returns the result record."""
+    if logits_t.dim() != 2:
+        raise ValueError("logits must be [n_rows, P]")
+    n_rows, P = logits_t.shape
+    x = _check_tensor(logits_t, torch.float32, "logits")
+    d = x if dlogits is None else _check_tensor(dlogits, torch.float32, "dlogits")
+    if dlogits is not None and tuple(dlogits.shape) != (n_rows, P):
+        raise ValueError("dlogits must have the shape of logits")
+    if result is None:
+        result = new_result(logits_t.device)
+    if workspace is None:
+        workspace = logits_workspace(n_rows, logits_t.device)
+    _lib.check(_lib.lib().grpo_b200_logits(
+        x, d, _check_tensor(logp_old, torch.float32, "logp_old"), _check_tensor(logp_ref, torch.float32, "logp_ref"),
+        _check_tensor(selected, torch.int32, "selected"), _check_tensor(advantages, torch.float32, "advantages"),
+        _check_tensor(weights, torch.float32, "weights"), _check_tensor(mask, torch.int32, "mask"),
+        n_rows, row_offset, tokens_per_seq, V, P, float(clip_eps), float(beta), int(kernel), int(check_inputs),
+        None if selected_logp is None else _check_tensor(selected_logp, torch.float32, "selected_logp"),
+        _check_tensor(result, torch.float64, "result"), workspace.data_ptr(), workspace.numel(), _stream()))
+    return result
+
+
+def set_variant(variant: int) -> None:
+    """Force a row-resident kernel variant (index into :func:`variants`), ``-1`` for automatic."""
+    _lib.check(_lib.lib().grpo_b200_logits_set_variant(variant))
+
+
+def variants() -> list[str]:
+    out, i = [], 0
+    while True:
+        name = _lib.lib().grpo_b200_logits_variant_name(i)
+        if name is None:
+            return out
+        out.append(name.decode())
+        i += 1
+
+
+def plan(logits_t: torch.Tensor, V: int, kernel: int = CudaLogitsKernel.fused,
+         dlogits: torch.Tensor | None = None) -> str:
+    """Name of the kernel the dispatcher runs for this layout."""
+    d = logits_t if dlogits is None else dlogits
+    return _lib.lib().grpo_b200_logits_plan(logits_t.data_ptr(), d.data_ptr(), V, logits_t.shape[1],
+                                            int(kernel)).decode()
+
+
+class ResidentBoundary:
+    """The whole loss boundary with nothing on the host: mask -> lengths -> weights -> fused logits
+    kernel -> result record, all enqueued on the current stream.  Buffers are allocated once."""
+
+    def __init__(self, n_seq: int, tokens_per_seq: int, V: int, P: int, *, clip_eps: float = 0.2,
+                 beta: float = 0.0, reduction: int = ReductionMode.sequence_mean, length_alpha: float = 0.0,
+                 device=None):
+        self.S, self.T, self.V, self.P = n_seq, tokens_per_seq, V, P
+        self.clip_eps, self.beta, self.reduction, self.alpha = clip_eps, beta, int(reduction), length_alpha
+        dev = device or torch.cuda.current_device()
+        self.lengths = torch.empty(n_seq, dtype=torch.int32, device=dev)
+        self.weights = torch.empty(n_seq, dtype=torch.float32, device=dev)
+        self.meta = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.result = new_result(dev)
+        self.workspace = logits_workspace(n_seq * tokens_per_seq, dev)
+
+    def __call__(self, logits_t, logp_old, logp_ref, selected, advantages, mask,
+                 kernel: int = CudaLogitsKernel.fused) -> torch.Tensor:
+        count_lengths(mask, self.S, self.T, 0, self.lengths)
+        weights_from_lengths(self.lengths, self.reduction, self.alpha, self.weights, self.meta)
+        return logits(logits_t, logp_old, logp_ref, selected, advantages, self.weights, mask, self.T, self.V,
+                      self.clip_eps, self.beta, kernel=kernel, result=self.result, workspace=self.workspace)

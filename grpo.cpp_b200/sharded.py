@@ -1,0 +1,100 @@
+"""Token-sharded execution of the logits path over ``torch.distributed`` (one process per GPU).
+
+The batch of ``N = S*T`` token rows is cut into contiguous row ranges, one per rank; a response
+may straddle two ranks.  Rows are independent given the per-response weight, so only two tiny
+exchanges exist, both plain sum all-reduces (NCCL over NVLink on GPUs):
+
+1. before the kernel: the per-response valid-token counts (``int32[S]``), so that every rank
+   derives the same global lengths, the same token-count normaliser and the same weights;
+2. after the kernel: the result record (``float64[5]``: loss, pg, kl and the two error counts).
+
+``dL/dlogits`` needs no communication.  The reference has no collective inside its loss path: its
+two-GPU demo shards whole responses under ``sequence_mean`` and divides by the device count on
+the host (apps/03_two_gpu_train.cu:200-215,247-281); token sharding with ``token_mean`` or
+``length_weighted`` needs the global lengths, which is what exchange 1 provides.
+
+``prepare`` depends only on the mask, so it runs once per rollout batch; ``step`` runs once per
+optimisation pass over that batch.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .api import CudaLogitsKernel, ReductionMode
+
+
+def shard_rows(n_rows: int, world: int, rank: int) -> tuple[int, int]:
+    """``(row_offset, row_count)`` of ``rank``: contiguous, sizes differ by at most one row."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("rank must lie in [0, world)")
+    base, rem = divmod(n_rows, world)
+    return rank * base + min(rank, rem), base + (1 if rank < rem else 0)
+
+
+class ShardedBoundary:
+    """One rank's view of the sharded loss boundary.
+
+    ``ops`` is the module providing ``count_lengths``, ``weights_from_lengths``, ``logits``,
+    ``new_result`` and ``logits_workspace`` (default: :mod:`.device`, the CUDA library).  The
+    indirection exists so that the rank logic -- offsets, exchanges, error propagation -- can be
+    exercised with CPU tensors over the ``gloo`` backend.
+    """
+
+    def __init__(self, n_seq: int, tokens_per_seq: int, V: int, P: int, *, clip_eps: float = 0.2,
+                 beta: float = 0.0, reduction: int = ReductionMode.token_mean, length_alpha: float = 0.0,
+                 group=None, ops=None, device=None):
+        if ops is None:
+            from . import device as ops  # the CUDA library; fails loudly when it is missing
+        self.ops = ops
+        self.S, self.T, self.V, self.P = n_seq, tokens_per_seq, V, P
+        self.clip_eps, self.beta, self.reduction, self.alpha = clip_eps, beta, int(reduction), length_alpha
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.row_offset, self.n_local = shard_rows(n_seq * tokens_per_seq, self.world, self.rank)
+        self.device = device
+        self.lengths = torch.zeros(n_seq, dtype=torch.int32, device=device)
+        self.weights = torch.zeros(n_seq, dtype=torch.float32, device=device)
+        self.meta = torch.zeros(2, dtype=torch.int32, device=device)
+        self.result = ops.new_result(device)
+        self.workspace = ops.logits_workspace(self.n_local, device)
+
+    def _all_reduce(self, t: torch.Tensor) -> None:
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+    def prepare(self, mask_local: torch.Tensor) -> None:
+        """Exchange 1: global lengths and weights from this rank's slice of the mask."""
+        if mask_local.numel() != self.n_local:
+            raise RuntimeError(f"mask has size {mask_local.numel()}, expected {self.n_local}")
+        self.ops.count_lengths(mask_local, self.S, self.T, self.row_offset, self.lengths)
+        self._all_reduce(self.lengths)
+        self.ops.weights_from_lengths(self.lengths, self.reduction, self.alpha, self.weights, self.meta)
+
+    def step(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
+             kernel: int = CudaLogitsKernel.fused) -> torch.Tensor:
+        """Kernel on the local rows (in place), then exchange 2.  Returns the global result record."""
+        self.ops.logits(logits_local, logp_old, logp_ref, selected, advantages, self.weights, mask_local,
+                        self.T, self.V, self.clip_eps, self.beta, row_offset=self.row_offset, kernel=kernel,
+                        result=self.result, workspace=self.workspace)
+        self._all_reduce(self.result)
+        return self.result
+
+    def stats(self) -> dict:
+        """Reads the records back (synchronises) and applies the reference's error contract
+        (src/cuda/grpo_loss_cuda.cu:44-46, 814-815) to the GLOBAL quantities."""
+        meta = self.meta.tolist()
+        res = self.result.tolist()
+        if meta[1] != 0:
+            raise RuntimeError("every sequence needs at least one valid token")
+        if res[4] != 0:
+            raise RuntimeError("selected token is outside the vocabulary")
+        loss, pg, kl = (float(torch.tensor(v, dtype=torch.float64).to(torch.float32)) for v in res[:3])
+        if not all(map(_finite, (loss, pg, kl))):
+            raise RuntimeError("CUDA logits loss became non-finite")
+        return {"loss": loss, "pg_loss": pg, "kl": kl, "valid_tokens": int(meta[0]), "bad_grads": int(res[3])}
+
+
+def _finite(x: float) -> bool:
+    return x == x and abs(x) != float("inf")

@@ -1,0 +1,71 @@
+// Public option and result types of the GRPO loss boundary, source-compatible with the
+// reference's include/grpo/grpo_loss.hpp (types at :10-43, shape guard at :46-67, index helpers at
+// :70-76) so that code written against the reference compiles unchanged against this library.
+//
+// This header declares data types only.  The reference's CPU functions (group_advantages_cpu,
+// grpo_loss_cpu, grpo_logits_cpu) are not part of this library: it has no CPU compute path.
+#pragma once
+
+#include <climits>
+#include <cstddef>
+#include <stdexcept>
+#include <vector>
+
+namespace grpo {
+
+// How rewards inside one prompt's group become advantages.
+enum class AdvantageMode { standardized, centered };
+
+// How per-token terms are weighted into the scalar loss:
+//   sequence_mean    each response weighs 1/S, its tokens share that equally
+//   token_mean       every valid token of the batch weighs 1/(number of valid tokens)
+//   length_weighted  a response of L valid tokens weighs L^alpha / S, shared equally by its tokens
+enum class ReductionMode { sequence_mean, token_mean, length_weighted };
+
+struct LossConfig {
+    float clip_eps = 0.2f;  // PPO clip half-width, in [0, 1)
+    float beta = 0.0f;      // weight of the KL term against the fixed reference policy, >= 0
+    ReductionMode reduction = ReductionMode::sequence_mean;
+    float length_alpha = 0.0f;  // exponent of length_weighted, in [0, 1]
+};
+
+struct LossStats {
+    float loss = 0.0f;     // pg_loss + beta * kl
+    float pg_loss = 0.0f;  // clipped policy-gradient surrogate
+    float kl = 0.0f;       // k3 estimate of KL(new || reference) on the sampled tokens
+    int valid_tokens = 0;  // number of mask == 1 tokens
+};
+
+struct LossResult {
+    LossStats stats;
+    std::vector<float> dlogp_new;  // dL/dlogp per token slot, 0 where masked
+};
+
+struct LogitsLossResult {
+    LossStats stats;
+    std::vector<float> dlogits;  // dL/dlogits, [B*G*T][V]
+};
+
+namespace detail {
+struct Shape {
+    std::size_t sequences;
+    std::size_t tokens;
+};
+
+// B*G responses and B*G*T token slots, both of which must fit an int.
+inline Shape checked_shape(int B, int G, int T) {
+    if (B <= 0 || G <= 0 || T <= 0) throw std::runtime_error("B, G and T must be positive");
+    const std::size_t limit = static_cast<std::size_t>(INT_MAX);
+    const std::size_t sequences = static_cast<std::size_t>(B) * static_cast<std::size_t>(G);
+    if (sequences > limit) throw std::runtime_error("sequence count exceeds INT_MAX");
+    const std::size_t tokens = sequences * static_cast<std::size_t>(T);
+    if (tokens > limit) throw std::runtime_error("token count exceeds INT_MAX");
+    return {sequences, tokens};
+}
+}  // namespace detail
+
+// Row-major positions in the [B][G] and [B][G][T] layouts.
+inline std::size_t idx2(int b, int g, int G) { return static_cast<std::size_t>(b) * G + g; }
+inline std::size_t idx3(int b, int g, int t, int G, int T) { return idx2(b, g, G) * T + t; }
+
+}  // namespace grpo

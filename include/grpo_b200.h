@@ -1,0 +1,230 @@
+/*
+ * grpo_b200.h -- C ABI of the B200-native GRPO loss boundary (libgrpo_b200.so).
+ *
+ * Two layers, both plain C (pointers and sizes, no C++ or framework types):
+ *
+ *   1. DEVICE layer  (grpo_b200_loss, grpo_b200_logits, ...): every pointer is a
+ *      device pointer on the current device.  These calls allocate nothing, never
+ *      synchronise and never exit the process: they validate their scalar
+ *      arguments, enqueue hand-written sm_100a kernels on the given stream and
+ *      return.  Results land in a small device record (grpo_b200_result_t) so a
+ *      caller can keep everything on the device, all-reduce it, or read it back.
+ *
+ *   2. HOST layer  (grpo_b200_*_host): the reference-facing calls.  They take the
+ *      same host arrays the reference's C++ API takes (as pointers + counts),
+ *      perform the reference's validation, copy to the device, run layer 1,
+ *      synchronise and copy back -- the exact contract of grpo::grpo_loss_cuda,
+ *      grpo::grpo_logits_cuda and grpo::grpo_logits_cuda_device_inplace.  The C++
+ *      functions in include/grpo/grpo_loss_cuda.cuh are thin wrappers over them.
+ *
+ * Each declaration cites the interface of the reference (KartikVashishta/grpo.cpp,
+ * paths relative to its root) that it replaces.
+ *
+ * There is no CPU fallback anywhere in this library: without a CUDA device every
+ * compute call fails with GRPO_B200_E_CUDA.
+ *
+ * Data layout shared by all calls (reference include/grpo/grpo_loss.hpp:70-76):
+ *   S = B*G responses, each padded to T token slots; N = S*T token rows, row i
+ *   belongs to response i / T.  mask[N] is int32 0/1 at arbitrary positions.
+ *   advantages[S], weights[S] are fp32.  Logits are N rows of P fp32 columns, of
+ *   which the first V are the vocabulary.
+ *
+ * Thread safety: all calls may be made concurrently from several host threads,
+ * each with its own current device (reference apps/03_two_gpu_train.cu:201-215).
+ */
+#ifndef GRPO_B200_H
+#define GRPO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A CUDA stream handle (cudaStream_t); NULL is the legacy default stream. */
+typedef struct CUstream_st* grpo_b200_stream_t;
+
+/* Return codes.  On a non-zero return grpo_b200_last_error() holds the text; for
+ * GRPO_B200_E_INVALID and GRPO_B200_E_NONFINITE it is, word for word, the message
+ * of the std::runtime_error the reference throws for the same condition. */
+enum {
+    GRPO_B200_OK = 0,
+    GRPO_B200_E_INVALID = 1,   /* argument / shape / value rejected (reference: throw) */
+    GRPO_B200_E_NONFINITE = 2, /* a result became non-finite (reference: throw) */
+    GRPO_B200_E_CUDA = 3,      /* CUDA runtime failure (reference: print + exit(1),
+                                  include/grpo/cuda_utils.cuh:8-16) */
+    GRPO_B200_E_WORKSPACE = 4  /* workspace pointer null or too small */
+};
+
+/* reference include/grpo/grpo_loss.hpp:15-19 */
+enum { GRPO_B200_SEQUENCE_MEAN = 0, GRPO_B200_TOKEN_MEAN = 1, GRPO_B200_LENGTH_WEIGHTED = 2 };
+/* reference include/grpo/grpo_loss_cuda.cuh:6-14.  Both values of each selector are accepted.
+ * The selected-token path has ONE kernel here (a deterministic shuffle/block/partials
+ * reduction with no global atomics), so ATOMIC and BLOCK_REDUCE run the same code.
+ * For the logits path FUSED picks the row-resident kernel (row held on chip, one read and one
+ * write of the logits) whenever the row layout allows it, SEPARATE forces the generic
+ * streaming kernel that also serves rows the resident kernel cannot take. */
+enum { GRPO_B200_LOSS_ATOMIC = 0, GRPO_B200_LOSS_BLOCK_REDUCE = 1 };
+enum { GRPO_B200_LOGITS_SEPARATE = 0, GRPO_B200_LOGITS_FUSED = 1 };
+/* reference include/grpo/grpo_loss.hpp:10-13 */
+enum { GRPO_B200_ADV_STANDARDIZED = 0, GRPO_B200_ADV_CENTERED = 1 };
+
+/* Device-side result record, written by the finalize step of each device call.
+ * Sums are accumulated in double from fp32 per-token products, in a fixed order:
+ * repeated runs on the same inputs give bit-identical records. */
+typedef struct {
+    double loss;      /* sum of weight * (pg + beta * kl) over active tokens   */
+    double pg_loss;   /* sum of weight * pg                                    */
+    double kl;        /* sum of weight * kl                                    */
+    double bad_grads; /* number of active tokens whose gradient is non-finite  */
+    double bad_inputs;/* selected-token path: active tokens with a non-finite log-probability or
+                         a mask value other than 0/1; logits path: active rows with an
+                         out-of-vocabulary selected id or (when checked) a non-finite logit */
+} grpo_b200_result_t;
+
+const char* grpo_b200_last_error(void);
+/* Library version and the architecture the kernels were compiled for ("sm_100a"). */
+const char* grpo_b200_build_info(void);
+
+/* ------------------------------------------------------------------------------------
+ * DEVICE LAYER
+ * ------------------------------------------------------------------------------------ */
+
+/* Per-response valid-token counts from the mask.
+ * Replaces the counting half of the reference's host-side make_weights
+ * (src/cuda/grpo_loss_cuda.cu:33-41; CPU twin src/cpu/grpo_loss.cpp:97-104).
+ * Counts the local rows [row_offset, row_offset + n_rows) of a batch of n_seq responses of
+ * tokens_per_seq slots each; lengths[n_seq] is fully written (0 for responses with no local
+ * row), so that per-rank partial counts of a token-sharded batch can be summed.  Any non-zero
+ * mask value counts as valid here, as in the reference's kernels; values other than 0/1 are
+ * reported by the loss calls through result->bad_inputs. */
+int grpo_b200_count_lengths(const int32_t* mask, int64_t n_rows, int64_t row_offset,
+                            int tokens_per_seq, int64_t n_seq, int32_t* lengths,
+                            grpo_b200_stream_t stream);
+
+/* Per-response token weights from (global) lengths.
+ * Replaces the weighting half of make_weights (src/cuda/grpo_loss_cuda.cu:43-55):
+ *   sequence_mean   1.0f / (float(S) * L_i)
+ *   token_mean      1.0f / float(sum L_i)
+ *   length_weighted powf(float(L_i), alpha - 1.0f) / float(S)
+ * meta[0] = sum of lengths (the reference's valid_tokens), meta[1] = number of responses with
+ * L_i == 0 (the reference throws "every sequence needs at least one valid token" for any). */
+int grpo_b200_weights_from_lengths(const int32_t* lengths, int64_t n_seq, int reduction,
+                                   float length_alpha, float* weights, int32_t* meta,
+                                   grpo_b200_stream_t stream);
+
+/* Group-relative advantages on the device.
+ * Replaces grpo::group_advantages_cpu (src/cpu/grpo_loss.cpp:16-58): per prompt, Welford mean
+ * and population variance in double, all-equal groups give exact zeros.  rewards[B*G] ->
+ * advantages[B*G]; meta[0] counts non-finite rewards or advantages. */
+int grpo_b200_group_advantages(const float* rewards, int B, int G, int mode, float eps,
+                               float* advantages, int32_t* meta, grpo_b200_stream_t stream);
+
+/* Selected-token path: masked per-token clipped policy-gradient + KL loss, dlogp and the three
+ * weighted sums.
+ * Replaces grpo_loss_block_kernel / grpo_loss_atomic_kernel and launch_loss
+ * (src/cuda/grpo_loss_cuda.cu:97-179, 527-549) including the accumulator reset the reference
+ * times with it (:834).  dlogp[n_tokens] is fully written (0 where masked).  The local tokens
+ * are [token_offset, token_offset + n_tokens) of the batch: token i belongs to response
+ * (token_offset + i) / tokens_per_seq, which indexes advantages[] and weights[].
+ * Uses workspace (grpo_b200_loss_workspace_bytes) for per-block partial sums. */
+size_t grpo_b200_loss_workspace_bytes(int64_t n_tokens);
+int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* logp_ref,
+                   const float* advantages, const float* weights, const int32_t* mask,
+                   int64_t n_tokens, int64_t token_offset, int tokens_per_seq,
+                   float clip_eps, float beta, float* dlogp, grpo_b200_result_t* result,
+                   void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream);
+
+/* Logits path: per active row log-softmax (max + normaliser), gather of the selected logit,
+ * token loss, and the log-softmax backward dL/dlogits = dlogp * (onehot - softmax); columns
+ * [V, P) and every masked row are written as zeros; masked rows and their selected id are
+ * never read.
+ * Replaces grpo_logits_fused_kernel, selected_logp_kernel + logits_backward_kernel and
+ * launch_logits (src/cuda/grpo_loss_cuda.cu:181-349, 551-582).  dlogits may equal logits
+ * (in place, the contract of grpo_logits_cuda_device_inplace, :774-817) or be a separate
+ * buffer of the same row stride P.  Rows are the local rows [row_offset, row_offset + n_rows).
+ * kernel: GRPO_B200_LOGITS_FUSED or _SEPARATE.  check_inputs != 0 additionally records rows
+ * with a non-finite logit or an out-of-range selected id in result->bad_inputs.
+ * selected_logp (nullable) receives log p(selected) per row (0 for masked rows). */
+size_t grpo_b200_logits_workspace_bytes(int64_t n_rows);
+int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
+                     const float* logp_ref, const int32_t* selected, const float* advantages,
+                     const float* weights, const int32_t* mask, int64_t n_rows, int64_t row_offset,
+                     int tokens_per_seq, int V, int P, float clip_eps, float beta, int kernel,
+                     int check_inputs, float* selected_logp, grpo_b200_result_t* result,
+                     void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream);
+
+/* Tuning hook for benchmarks: force the row-resident kernel variant (index into the table
+ * printed by grpo_b200_logits_variant_name), or -1 for the built-in choice.  Process-wide. */
+int grpo_b200_logits_set_variant(int variant);
+/* Name ("cluster x threads x vec") of variant i, NULL past the end of the table. */
+const char* grpo_b200_logits_variant_name(int variant);
+/* Name of the kernel the dispatcher would run for this row layout and selector. */
+const char* grpo_b200_logits_plan(const void* logits, const void* dlogits, int V, int P, int kernel);
+
+/* ------------------------------------------------------------------------------------
+ * HOST LAYER (reference-facing; host arrays in, host results out, synchronous)
+ * ------------------------------------------------------------------------------------ */
+
+/* Replaces grpo::grpo_loss_cuda (include/grpo/grpo_loss_cuda.cuh:26-37,
+ * src/cuda/grpo_loss_cuda.cu:620-660).  n_* are the element counts of the caller's arrays
+ * (the reference's std::vector sizes, checked the same way).  stats_out = {loss, pg_loss, kl}. */
+int grpo_b200_loss_host(const float* logp_new, size_t n_logp_new, const float* logp_old,
+                        size_t n_logp_old, const float* logp_ref, size_t n_logp_ref,
+                        const float* advantages, size_t n_advantages, const int32_t* mask,
+                        size_t n_mask, int B, int G, int T, float clip_eps, float beta,
+                        int reduction, float length_alpha, int kernel, float* dlogp_out,
+                        float* stats_out, int* valid_tokens_out);
+
+/* Replaces grpo::grpo_logits_cuda (include/grpo/grpo_loss_cuda.cuh:53-66,
+ * src/cuda/grpo_loss_cuda.cu:726-772): dense host logits [N][V] in, host dlogits [N][V] out. */
+int grpo_b200_logits_host(const float* logits, size_t n_logits, const float* logp_old,
+                          size_t n_logp_old, const float* logp_ref, size_t n_logp_ref,
+                          const int32_t* selected, size_t n_selected, const float* advantages,
+                          size_t n_advantages, const int32_t* mask, size_t n_mask, int B, int G,
+                          int T, int V, float clip_eps, float beta, int reduction,
+                          float length_alpha, int kernel, float* dlogits_out, float* stats_out,
+                          int* valid_tokens_out);
+
+/* Replaces grpo::grpo_logits_cuda_device_inplace (include/grpo/grpo_loss_cuda.cuh:68-86,
+ * src/cuda/grpo_loss_cuda.cu:774-817): logits_and_dlogits is a caller-owned DEVICE pointer to
+ * N rows of P floats on the current device, replaced in place by dL/dlogits; the per-token
+ * metadata are host arrays.  Returns after the device work is complete. */
+int grpo_b200_logits_device_inplace_host(float* logits_and_dlogits, const float* logp_old,
+                                         size_t n_logp_old, const float* logp_ref,
+                                         size_t n_logp_ref, const int32_t* selected,
+                                         size_t n_selected, const float* advantages,
+                                         size_t n_advantages, const int32_t* mask, size_t n_mask,
+                                         int B, int G, int T, int V, int P, float clip_eps,
+                                         float beta, int reduction, float length_alpha, int kernel,
+                                         float* stats_out, int* valid_tokens_out);
+
+/* Replaces grpo::benchmark_grpo_loss_cuda (include/grpo/grpo_loss_cuda.cuh:39-51,
+ * src/cuda/grpo_loss_cuda.cu:819-886): resident arrays, `warmup` passes, then the median of 7
+ * repeats of `iterations` back-to-back passes per selector, in ms per pass. */
+int grpo_b200_benchmark_loss_host(const float* logp_new, size_t n_logp_new, const float* logp_old,
+                                  size_t n_logp_old, const float* logp_ref, size_t n_logp_ref,
+                                  const float* advantages, size_t n_advantages,
+                                  const int32_t* mask, size_t n_mask, int B, int G, int T,
+                                  float clip_eps, float beta, int reduction, float length_alpha,
+                                  int warmup, int iterations, float* atomic_ms, float* block_ms);
+
+/* Replaces grpo::benchmark_grpo_logits_cuda (include/grpo/grpo_loss_cuda.cuh:88-102,
+ * src/cuda/grpo_loss_cuda.cu:888-975): separate input and output logits buffers with P = V,
+ * 15 samples in alternating order, medians in ms per pass. */
+int grpo_b200_benchmark_logits_host(const float* logits, size_t n_logits, const float* logp_old,
+                                    size_t n_logp_old, const float* logp_ref, size_t n_logp_ref,
+                                    const int32_t* selected, size_t n_selected,
+                                    const float* advantages, size_t n_advantages,
+                                    const int32_t* mask, size_t n_mask, int B, int G, int T, int V,
+                                    float clip_eps, float beta, int reduction, float length_alpha,
+                                    int warmup, int iterations, float* separate_ms, float* fused_ms);
+
+/* Frees the calling thread's current device's cached workspace and staging buffers. */
+int grpo_b200_release_cache(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRPO_B200_H */

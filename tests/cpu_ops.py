@@ -1,0 +1,67 @@
+"""CPU stand-in for ``grpo_cpp_b200.device`` -- TEST ONLY.
+
+Lets the rank logic of ``grpo_cpp_b200.sharded`` (row offsets, the two all-reduces, error
+propagation) run under the ``gloo`` backend on a machine without a GPU.  Per-row arithmetic is
+delegated to the CPU oracle one row at a time (a 1x1x1 batch has weight exactly 1), then scaled
+by the rank-agreed weight.  The product never imports this module.
+"""
+import numpy as np
+import torch
+
+import oracle_py
+
+
+def new_result(device=None):
+    return torch.zeros(5, dtype=torch.float64)
+
+
+def logits_workspace(n_rows, device=None):
+    return torch.empty(0, dtype=torch.uint8)
+
+
+def count_lengths(mask, n_seq, tokens_per_seq, row_offset=0, out=None):
+    m = mask.numpy()
+    seq = (row_offset + np.arange(m.size)) // tokens_per_seq
+    counts = np.bincount(seq[m != 0], minlength=n_seq).astype(np.int32)
+    if out is None:
+        return torch.from_numpy(counts)
+    out.copy_(torch.from_numpy(counts))
+    return out
+
+
+def weights_from_lengths(lengths, reduction, length_alpha=0.0, out=None, meta=None):
+    L = lengths.numpy()
+    f = np.float32
+    S = f(L.size)
+    with np.errstate(divide="ignore"):
+        if reduction == 0:
+            w = f(1.0) / (S * L.astype(f))
+        elif reduction == 1:
+            w = np.full(L.size, f(1.0) / f(int(L.sum())), f)
+        else:
+            w = np.power(L.astype(f), f(length_alpha) - f(1.0)) / S
+    w = np.where(L > 0, w, 0).astype(f)
+    out.copy_(torch.from_numpy(w))
+    meta.copy_(torch.tensor([int(L.sum()), int((L == 0).sum())], dtype=torch.int32))
+    return out, meta
+
+
+def logits(logits_t, logp_old, logp_ref, selected, advantages, weights, mask, tokens_per_seq, V, clip_eps, beta,
+           *, row_offset=0, kernel=1, result=None, workspace=None, **_):
+    port = oracle_py.load("port")
+    x = logits_t.numpy()
+    n_rows, P = x.shape
+    total = np.zeros(5)
+    for r in range(n_rows):
+        if mask[r].item() == 0:
+            x[r, :] = 0.0
+            continue
+        seq = (row_offset + r) // tokens_per_seq
+        w = np.float32(weights[seq].item())
+        stats, _, d = port.logits(x[r, :V].copy(), [logp_old[r].item()], [logp_ref[r].item()], [selected[r].item()],
+                                  [advantages[seq].item()], [1], 1, 1, 1, V, clip_eps, beta, 0, 0.0)
+        total[:3] += (w * stats.astype(np.float32)).astype(np.float64)
+        x[r, :V] = w * d[0]
+        x[r, V:] = 0.0
+    result.copy_(torch.from_numpy(total))
+    return result
