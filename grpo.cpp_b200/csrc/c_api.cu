@@ -132,7 +132,8 @@ int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* lo
 }
 
 size_t grpo_b200_logits_workspace_bytes(int64_t n_rows) {
-    return n_rows > 0 ? static_cast<size_t>(n_rows) * sizeof(float4) : 0;  // per-row loss terms
+    // one 32-byte record per row, then one 32-byte slot for the kernel's status word
+    return n_rows > 0 ? static_cast<size_t>(n_rows) * sizeof(RowRecord) + 32 : 0;
 }
 
 int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
@@ -151,8 +152,8 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
         return invalid("unknown logits kernel selector");
     if (int rc = check_options(clip_eps, beta)) return rc;
     if (!workspace || workspace_bytes < grpo_b200_logits_workspace_bytes(n_rows) ||
-        (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
-        set_error("workspace must be 16-byte aligned and hold grpo_b200_logits_workspace_bytes() bytes");
+        (reinterpret_cast<uintptr_t>(workspace) & 31u)) {
+        set_error("workspace must be 32-byte aligned and hold grpo_b200_logits_workspace_bytes() bytes");
         return GRPO_B200_E_WORKSPACE;
     }
     LogitsArgs a;
@@ -171,15 +172,18 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
     a.P = P;
     a.clip_eps = clip_eps;
     a.beta = beta;
-    a.row_terms = static_cast<float4*>(workspace);
+    a.rows = static_cast<RowRecord*>(workspace);
     a.selected_logp = selected_logp;
     a.result = result;
+    a.status = reinterpret_cast<int*>(a.rows + n_rows);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    GRPO_CUDA_TRY(cudaMemsetAsync(a.status, 0, 16, s));
     const int variant = kernel == GRPO_B200_LOGITS_FUSED ? pick_resident_variant(logits, dlogits, V, P) : -1;
     if (variant >= 0)
         GRPO_CUDA_TRY(launch_logits_resident(variant, check_inputs != 0, a, s));
     else
         GRPO_CUDA_TRY(launch_logits_streaming(check_inputs != 0, a, s));
+    GRPO_CUDA_TRY(launch_logits_terms(a, s));
     GRPO_CUDA_TRY(launch_logits_finalize(a, s));
     return GRPO_B200_OK;
 }

@@ -28,19 +28,14 @@ struct TokenTerms {
     float loss, pg, kl, grad;
 };
 
-// PRECISE = true evaluates exp / expm1 in double and rounds to fp32 (matches a correctly
-// rounded libm expf in all but the rarest cases; used where there is one token per row of
-// logits).  PRECISE = false uses the fp32 device functions (<= 2 ulp), for the path that runs
-// millions of tokens per launch.
-template <bool PRECISE>
-__device__ __forceinline__ TokenTerms token_terms(float lp_new, float lp_old, float lp_ref,
-                                                  float adv, float w, float clip_eps, float beta) {
+// Everything after the two transcendental calls: rho = exp(lp_new - lp_old) (read only when the
+// advantage is non-zero), em1 = expm1(d), d = lp_ref - lp_new.
+__device__ __forceinline__ TokenTerms token_assemble(float rho, float em1, float d, float adv, float w,
+                                                     float clip_eps, float beta) {
     const float lo = __fsub_rn(1.0f, clip_eps);
     const float hi = __fadd_rn(1.0f, clip_eps);
     float pg = 0.0f, pg_grad = 0.0f;
-    if (adv != 0.0f) {  // a zero advantage never evaluates the ratio (overflow-safe)
-        const float a = __fsub_rn(lp_new, lp_old);
-        const float rho = PRECISE ? static_cast<float>(exp(static_cast<double>(a))) : expf(a);
+    if (adv != 0.0f) {  // a zero advantage never looks at the ratio (overflow-safe)
         const float rho_c = rho < lo ? lo : (hi < rho ? hi : rho);
         const float u = __fmul_rn(rho, adv);
         const float c = __fmul_rn(rho_c, adv);
@@ -50,8 +45,6 @@ __device__ __forceinline__ TokenTerms token_terms(float lp_new, float lp_old, fl
         const bool cut = (adv > 0.0f && rho > hi) || (adv < 0.0f && rho < lo);
         pg_grad = cut ? 0.0f : __fmul_rn(-adv, rho);
     }
-    const float d = __fsub_rn(lp_ref, lp_new);
-    const float em1 = PRECISE ? static_cast<float>(expm1(static_cast<double>(d))) : expm1f(d);
     const float kl = __fsub_rn(em1, d);  // k3 estimator: e^d - 1 - d >= 0
     const float loss = __fadd_rn(pg, __fmul_rn(beta, kl));
     const float kl_grad = __fmul_rn(-beta, em1);
@@ -61,6 +54,23 @@ __device__ __forceinline__ TokenTerms token_terms(float lp_new, float lp_old, fl
     t.kl = __fmul_rn(w, kl);
     t.grad = __fmul_rn(w, __fadd_rn(pg_grad, kl_grad));
     return t;
+}
+
+// PRECISE = true evaluates exp / expm1 in double and rounds to fp32 (matches a correctly
+// rounded libm expf in all but the rarest cases; used where there is one token per row of
+// logits).  PRECISE = false uses the fp32 device functions (<= 2 ulp), for the path that runs
+// millions of tokens per launch.
+template <bool PRECISE>
+__device__ __forceinline__ TokenTerms token_terms(float lp_new, float lp_old, float lp_ref,
+                                                  float adv, float w, float clip_eps, float beta) {
+    float rho = 1.0f;
+    if (adv != 0.0f) {
+        const float a = __fsub_rn(lp_new, lp_old);
+        rho = PRECISE ? static_cast<float>(exp(static_cast<double>(a))) : expf(a);
+    }
+    const float d = __fsub_rn(lp_ref, lp_new);
+    const float em1 = PRECISE ? static_cast<float>(expm1(static_cast<double>(d))) : expm1f(d);
+    return token_assemble(rho, em1, d, adv, w, clip_eps, beta);
 }
 
 __device__ __forceinline__ bool finite_f(float x) { return fabsf(x) <= 3.402823466e+38f; }
@@ -126,6 +136,17 @@ struct LossArgs {
 int loss_grid_blocks(long long n_tokens);
 cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream);
 
+// What the row kernels leave per active row for the terms kernel: the normaliser (relative to
+// e^m, double), the row maximum, the gathered selected logit and the input-error flags.  The
+// terms kernel overwrites the first 16 bytes with {w*loss, w*pg, w*kl, flags} for the final sum.
+struct __align__(32) RowRecord {
+    double z;
+    float m;
+    float x_sel;
+    float flags;
+    float pad[3];
+};
+
 struct LogitsArgs {
     const float* logits;
     float* dlogits;
@@ -140,9 +161,10 @@ struct LogitsArgs {
     int tokens_per_seq;
     int V, P;
     float clip_eps, beta;
-    float4* row_terms;  // [n_rows] {w*loss, w*pg, w*kl, flags}
+    RowRecord* rows;    // [n_rows] per-row hand-over between the row kernel and the terms kernel
     float* selected_logp;
     grpo_b200_result_t* result;
+    int* status;  // set non-zero when a bounded pipeline wait gave up
 };
 // flags stored in row_terms.w (small integers, exact in fp32)
 constexpr float kRowBadGrad = 1.0f;
@@ -154,6 +176,7 @@ int resident_variant_count();
 extern int g_forced_variant;
 cudaError_t launch_logits_resident(int variant, bool check, const LogitsArgs& a, cudaStream_t stream);
 cudaError_t launch_logits_streaming(bool check, const LogitsArgs& a, cudaStream_t stream);
+cudaError_t launch_logits_terms(const LogitsArgs& a, cudaStream_t stream);
 cudaError_t launch_logits_finalize(const LogitsArgs& a, cudaStream_t stream);
 
 cudaError_t launch_count_lengths(const int32_t* mask, long long n_rows, long long row_offset,

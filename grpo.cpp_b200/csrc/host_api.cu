@@ -214,6 +214,10 @@ int check_selected(const int32_t* selected, const int32_t* mask, size_t n, int V
 }
 
 int fill_stats(const grpo_b200_result_t& r, float* stats, const char* what) {
+    if (r.bad_inputs < 0.0) {  // the kernel's bounded pipeline wait gave up
+        set_error("CUDA error: logits kernel abandoned a stalled copy pipeline");
+        return GRPO_B200_E_CUDA;
+    }
     stats[0] = static_cast<float>(r.loss);
     stats[1] = static_cast<float>(r.pg_loss);
     stats[2] = static_cast<float>(r.kl);
@@ -434,7 +438,7 @@ int grpo_b200_logits_host(const float* logits, size_t n_logits, const float* log
     GRPO_CUDA_TRY(cudaMemcpyAsync(m.result_h, m.result_d, sizeof(*m.result_h), cudaMemcpyDeviceToHost, nullptr));
     GRPO_CUDA_TRY(cudaMemcpyAsync(dlogits_out, logits_d, total * 4, cudaMemcpyDeviceToHost, nullptr));
     GRPO_CUDA_TRY(cudaStreamSynchronize(nullptr));
-    if (m.result_h->bad_inputs != 0.0) return invalid("logits must be finite");
+    if (m.result_h->bad_inputs > 0.0) return invalid("logits must be finite");
     *valid_tokens_out = valid;
     if (int rc = fill_stats(*m.result_h, stats_out, "CUDA logits loss became non-finite")) return rc;
     if (m.result_h->bad_grads != 0.0) return nonfinite("CUDA logits gradient became non-finite");

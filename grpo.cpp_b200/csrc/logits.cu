@@ -2,22 +2,40 @@
 // backward in one pass, writing dL/dlogits over the logits.
 //
 // Replaces grpo_logits_fused_kernel and the three-kernel "separate" pipeline of the reference
-// (src/cuda/grpo_loss_cuda.cu:181-349).  Two kernels live here:
+// (src/cuda/grpo_loss_cuda.cu:181-349).  Two kernels live here.
 //
-//  * the ROW-RESIDENT kernel: a thread-block cluster of CLUSTER CTAs owns one row; every
-//    thread keeps VEC float4 chunks of the row in registers, so the row is read from HBM once
-//    (128-bit streaming loads), reduced on chip (registers -> warp shuffles -> shared memory
-//    -> distributed shared memory across the cluster), and the gradient is written straight
-//    from the same registers (128-bit streaming stores).  One exp per element: the thread's
-//    e_i = 2^((x_i - m_thread) * log2 e) are kept and rescaled by one per-thread factor
-//    once the row maximum and normaliser are known.
-//  * the STREAMING kernel: one CTA per row, three sweeps over the row (max, normaliser,
-//    gradient; the second and third come from L2 for rows of ordinary size).  It takes any V, P
-//    and alignment, and is what GRPO_B200_LOGITS_SEPARATE selects.
+// PIPELINED kernel (what GRPO_B200_LOGITS_FUSED runs whenever the layout allows):
+//   * persistent: one CTA per SM (or a thread-block cluster of 2/4/8 CTAs for rows that do not
+//     fit one CTA's registers) walks rows cluster_id, cluster_id + n_clusters, ...;
+//   * a ring of shared-memory stages is filled by bulk asynchronous copies
+//     (cp.async.bulk global -> shared, completion on an mbarrier) issued by one elected thread
+//     up to STAGES tiles ahead, so the next rows stream in from HBM while the current row is
+//     being reduced and written back -- the copy engine, not thread occupancy, hides latency;
+//   * each thread lifts its chunks from the ring into registers (128-bit LDS), releases the
+//     stage, and keeps the row slice in registers until the gradient is stored (128-bit
+//     streaming stores): one HBM read and one HBM write per logit, one exp per element;
+//   * the row reduction runs registers -> warp shuffles -> shared memory -> distributed shared
+//     memory across the cluster; no global atomics.
+//   Every bulk copy has a single destination CTA (its issuer).
+//
+// STREAMING kernel (GRPO_B200_LOGITS_SEPARATE, and any layout the pipelined kernel cannot take:
+// P not a multiple of 4, unaligned base, rows beyond the largest cluster): one CTA per row,
+// sweeps over global memory (max, normaliser, correction, gradient), later sweeps from L2.
+//
+// Accuracy of the log-sum-exp.  The token loss is a cancelling sum and the reference rounds
+// log p(selected) to fp32, so the normaliser has to agree with the reference's double
+// arithmetic to about 1e-8 relative or rows round differently.  Both kernels therefore
+//   (1) evaluate e_i = 2^(x_i*log2e - shift) with a two-constant log2e and one FMA residual so
+//       the exponent itself carries no systematic error,
+//   (2) accumulate the e_i in double (fixed trees), combining per-warp partial sums with
+//       factors computed in double, and
+//   (3) recompute in double the few elements that each carry more than 1/256 of the
+//       normaliser (at most 256 per row; none when the row is flat) and correct the sum.
+// The gradient itself only needs the fp32 e_i.
 //
 // Neither kernel touches a masked row's logits or selected id; both write zeros over all P
-// columns of a masked row and over columns [V, P) of an active one.  Per-row loss terms go to
-// a workspace and are summed in a fixed order by a finalize kernel: no atomics anywhere.
+// columns of a masked row and over columns [V, P) of an active one.  Per-row loss terms go to a
+// workspace and are summed in a fixed order by a finalize kernel.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -28,279 +46,555 @@ namespace grpo_b200 {
 
 int g_forced_variant = -1;
 
+// Build-time diagnostic (-DGRPO_TIMELINE): CTA 0 records the SM clock at the phase boundaries of
+// its first rows, for threads 0 and THREADS-1, into a device array that a debug call copies out.
+#ifdef GRPO_TIMELINE
+__device__ long long g_timeline[2][16][8];
+#define GRPO_TL(phase)                                                                          \
+    do {                                                                                        \
+        if (blockIdx.x == 0 && (tid == 0 || tid == THREADS - 1) && tl_row < 16)                 \
+            g_timeline[tid == 0 ? 0 : 1][tl_row][phase] = clock64();                            \
+        if ((phase) == 7) tl_row++;                                                             \
+    } while (0)
+#else
+#define GRPO_TL(phase) do { } while (0)
+#endif
+
 namespace {
 
-struct RowStat {
-    float m;  // running maximum (-inf when empty)
-    float s;  // sum of 2^((x - m) * log2 e) (0 when empty)
-};
+#define kNegInf (-CUDART_INF_F)
+// log2(e) split into an fp32 head and tail: kLog2eHi + kLog2eLo = log2(e) to ~1e-16
+constexpr float kLog2eHi = 1.4426950216293335f;
+constexpr float kLog2eLo = 1.9259629911e-8f;
+constexpr double kLog2eD = 1.4426950408889634073599246810019;
+constexpr double kHeavyFraction = 1.0 / 256.0;  // elements above this share of the normaliser are redone in double
+// Mean relative error of ex2.approx.ftz.f32 on this architecture, measured over 4M arguments in
+// [-16, -1]: -4.9e-8 (rms 5.8e-8, max 1.4e-7).  The hardware result is that much low on average,
+// so sums of such terms are scaled back up; elements redone in double are exempt.
+constexpr double kEx2BiasFix = 1.0 + 4.9e-8;
 
-// Merge of two (max, normaliser) pairs.  Symmetric in its arguments, so a butterfly leaves the
-// same bits in every lane.  An empty side (m = -inf, s = 0) contributes exactly 0.
-__device__ __forceinline__ RowStat merge(RowStat a, RowStat b) {
-    RowStat r;
-    r.m = fmaxf(a.m, b.m);
-    const float ref = r.m == -CUDART_INF_F ? 0.0f : r.m;
-    r.s = a.s * ex2_approx((a.m - ref) * kLog2e) + b.s * ex2_approx((b.m - ref) * kLog2e);
-    return r;
+// e = 2^(x*log2e - shift): head product and subtraction in one FMA, tail in a second
+__device__ __forceinline__ float exp_rel(float x, float shift) {
+    return ex2_approx(fmaf(x, kLog2eLo, fmaf(x, kLog2eHi, -shift)));
 }
 
-__device__ __forceinline__ RowStat warp_merge(RowStat v) {
+__device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        RowStat other;
-        other.m = __shfl_xor_sync(0xffffffffu, v.m, o);
-        other.s = __shfl_xor_sync(0xffffffffu, v.s, o);
-        v = merge(v, other);
-    }
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
 
-// What the row leader hands to every thread of its CTA for the backward sweep.
-struct RowBroadcast {
-    float row_max;      // M
-    float neg_g_over_z; // -dlogp / normaliser (normaliser relative to e^M)
-    float g;            // dlogp
-    int selected;
-};
-
-// 2^(x*log2e - shift) with shift = fl(m*log2e) differs from e^(x-m) by the factor 2^delta,
-// delta = m*log2e - shift, which one FMA recovers exactly.  Returns 2^(-delta) (to first order,
-// |delta| < 2^-18), the factor that converts such terms to "relative to e^m".
-__device__ __forceinline__ float shift_correction(float m_ref, float shift) {
-    const float delta = fmaf(m_ref, kLog2e, -shift);
-    return fmaf(-delta, 0.69314718f, 1.0f);
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
 }
 
-// Row-level scalar work, done by one thread per CTA: log-sum-exp in double, selected
-// log-probability, token loss.  Follows src/cpu/grpo_loss.cpp:214-215 and :137-160.
-__device__ __forceinline__ RowBroadcast row_leader(const LogitsArgs& a, long long row, RowStat st, float x_sel,
-                                                   int sel, bool bad_input, bool write_terms) {
-    const long long seq = (a.row_offset + row) / a.tokens_per_seq;
-    const double lse = static_cast<double>(st.m) + log(static_cast<double>(st.s));
-    const float lp_new = static_cast<float>(static_cast<double>(x_sel) - lse);
-    const float adv = __ldg(a.advantages + seq);
-    const float w = __ldg(a.weights + seq);
-    const TokenTerms t = token_terms<true>(lp_new, __ldg(a.logp_old + row), __ldg(a.logp_ref + row), adv, w,
-                                           a.clip_eps, a.beta);
-    RowBroadcast b;
-    b.row_max = st.m;
-    b.g = t.grad;
-    b.neg_g_over_z = -t.grad / st.s;
-    b.selected = sel;
-    if (write_terms) {
-        float flags = 0.0f;
-        if (!finite_f(t.grad) || !finite_f(b.neg_g_over_z)) flags += kRowBadGrad;
-        if (bad_input) flags += kRowBadInput;
-        a.row_terms[row] = make_float4(t.loss, t.pg, t.kl, flags);
-        if (a.selected_logp) a.selected_logp[row] = lp_new;
-    }
-    return b;
+// all-lanes double sum with a fixed butterfly (commutative pairs: same bits in every lane)
+__device__ __forceinline__ double warp_sum_all(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Kahan step: (s, c) += v with the rounding error of each addition carried in c; the running
+// total is s - c.  Plain fp32 adds, never re-associated by the compiler without fast-math.
+__device__ __forceinline__ void kahan_add(float& s, float& c, float v) {
+    const float y = __fsub_rn(v, c);
+    const float t = __fadd_rn(s, y);
+    c = __fsub_rn(__fsub_rn(t, s), y);
+    s = t;
 }
 
 __device__ __forceinline__ float max4(float4 v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
 
+// What the row leader hands to every thread of its CTA for the backward sweep.
+struct RowBroadcast {
+    float neg_g_over_z;  // -dlogp / normaliser (normaliser relative to e^M)
+    float g;             // dlogp
+    int selected;
+};
+
+// Per-row scalars the leader needs, fetched at the start of the row so that their latency is
+// hidden behind the row's loads.
+struct RowScalars {
+    float lp_old, lp_ref, adv, w;
+};
+
+__device__ __forceinline__ RowScalars load_row_scalars(const LogitsArgs& a, long long row) {
+    const long long seq = (a.row_offset + row) / a.tokens_per_seq;
+    RowScalars r;
+    r.lp_old = __ldg(a.logp_old + row);
+    r.lp_ref = __ldg(a.logp_ref + row);
+    r.adv = __ldg(a.advantages + seq);
+    r.w = __ldg(a.weights + seq);
+    return r;
+}
+
+// The row's serial section, kept short: dlogp for the backward sweep from fp32 device math
+// (log, exp, expm1: a few ulp, far inside the gradient's tolerance), and the row record for the
+// terms kernel, which redoes the same step in double, off this kernel's critical path, for the
+// three loss sums (a cancelling sum that needs the reference's double log-sum-exp).
+// z is the normaliser relative to e^row_max.  Follows src/cpu/grpo_loss.cpp:214-215, :137-160.
+__device__ __forceinline__ RowBroadcast row_leader_fast(const LogitsArgs& a, long long row, float row_max, double z,
+                                                        float x_sel, int sel, const RowScalars& sc, bool bad_input,
+                                                        bool write_record) {
+    const float zf = static_cast<float>(z);
+    const float lp_new = x_sel - (row_max + logf(zf));
+    const TokenTerms t = token_terms<false>(lp_new, sc.lp_old, sc.lp_ref, sc.adv, sc.w, a.clip_eps, a.beta);
+    RowBroadcast b;
+    b.g = t.grad;
+    b.neg_g_over_z = -t.grad / zf;
+    b.selected = sel;
+    if (write_record) {
+        RowRecord r;
+        r.z = z;
+        r.m = row_max;
+        r.x_sel = x_sel;
+        r.flags = bad_input ? kRowBadInput : 0.0f;
+        r.pad[0] = r.pad[1] = r.pad[2] = 0.0f;
+        a.rows[row] = r;
+    }
+    return b;
+}
+
+// ---- mbarrier / bulk-copy primitives (sm_90+ PTX) ------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait: gives up after about two seconds of SM clock and reports failure, so a lost
+// copy can never hang the device.  The caller then stops touching the ring ("not alive") but
+// keeps meeting every block and cluster barrier until the kernel ends.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > (1LL << 32)) return false;
+    }
+    return true;
+}
+// global -> the issuing CTA's own shared memory, completion counted in bytes on `bar`
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+// Per-CTA partial of the row reduction, exchanged through distributed shared memory.
+struct Exchange {
+    double s;   // normaliser of the CTA's slice relative to e^m
+    float m;    // maximum of the slice (-inf when empty)
+    float chk;  // finiteness probe
+};
+
 // ---------------------------------------------------------------------------------------------
-// Row-resident kernel.  Requires P % 4 == 0 and 16-byte aligned row starts; the dispatcher
-// guarantees ceil(P/4 / CLUSTER) <= THREADS * VEC.
+// Pipelined kernel.  Requires P % 4 == 0 and 16-byte aligned bases; the dispatcher guarantees
+// ceil(P/4 / CLUSTER) <= THREADS * VEC.  TJ chunks per thread per ring stage, STAGES stages.
 // ---------------------------------------------------------------------------------------------
-template <int THREADS, int VEC, int CLUSTER, bool CHECK>
-__global__ void __launch_bounds__(THREADS) logits_resident_kernel(const LogitsArgs a) {
+template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, bool CHECK>
+__global__ void __launch_bounds__(THREADS, (VEC >= 16 ? 512 : 1024) / THREADS) logits_pipelined_kernel(const LogitsArgs a) {
     constexpr int WARPS = THREADS / 32;
-    __shared__ RowStat warp_stat[WARPS];
+    constexpr int TILE_CHUNKS = TJ * THREADS;
+    constexpr int TILES = VEC / TJ;
+    static_assert(VEC % TJ == 0, "tiles must cover the per-thread chunks exactly");
+    static_assert(WARPS <= 32 && CLUSTER <= 32, "one lane per warp / per cluster rank in the combine step");
+
+    extern __shared__ __align__(128) unsigned char ring_raw[];
+    float4* ring = reinterpret_cast<float4*>(ring_raw);
+    __shared__ uint64_t full_bar[STAGES];
+    __shared__ uint64_t empty_bar[STAGES];
+    __shared__ float warp_m[WARPS];
+    __shared__ float warp_shift[WARPS];
     __shared__ float warp_chk[WARPS];
-    __shared__ float4 exchange;  // this CTA's {m, s, finite-check, 0}, read by its cluster peers
+    __shared__ double warp_s[WARPS];
+    __shared__ double warp_f[WARPS];  // 2^(shift_w - M*log2e): the warp's terms relative to the row maximum
+    __shared__ double warp_d[WARPS];
+    __shared__ Exchange exchange[2][2];  // [row parity][reduction round]
+    __shared__ float row_max_sh;
+    __shared__ double row_z_sh;
+    __shared__ float row_chk_sh;
     __shared__ RowBroadcast bc;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    const long long row = blockIdx.x / CLUSTER;
     unsigned crank = 0;
     if (CLUSTER > 1) crank = cg::this_cluster().block_rank();
+    const long long cluster_id = blockIdx.x / CLUSTER;
+    const long long n_clusters = gridDim.x / CLUSTER;
 
+    const int V = a.V;
     const int P4 = a.P >> 2;
     const int per_cta = (P4 + CLUSTER - 1) / CLUSTER;
-    const int c0 = crank * per_cta;
-    const int c1 = min(c0 + per_cta, P4);
-    const float4* in = reinterpret_cast<const float4*>(a.logits + row * static_cast<long long>(a.P));
-    float4* out = reinterpret_cast<float4*>(a.dlogits + row * static_cast<long long>(a.P));
-    const int V = a.V;
+    const int c0 = crank * per_cta;                          // first chunk of this CTA's slice
+    const int c1 = min(c0 + per_cta, P4);                    // end of the slice (stores)
+    const int n_load = max(min(c1, (V + 3) >> 2) - c0, 0);   // chunks that hold vocabulary (loads)
+    const int n_tiles = (n_load + TILE_CHUNKS - 1) / TILE_CHUNKS;
+    // The single chunk that straddles column V (when V % 4 != 0) belongs to one thread of one CTA:
+    // special_j is its register index there, -1 everywhere else.
+    const int v_rem = V & 3;
+    int special_j = -1;
+    if (v_rem != 0) {
+        const int cs = (V >> 2) - c0;
+        if (cs >= 0 && cs < c1 - c0 && cs % THREADS == tid) special_j = cs / THREADS;
+    }
 
-    if (a.mask[row] == 0) {  // uniform over the cluster: nobody reaches a cluster barrier
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // producer cursor (meaningful in thread 0 only): next tile to request
+    long long p_row = cluster_id;
+    int p_tile = 0;
+    unsigned q_prod = 0;
+    if (tid == 0) {
+        while (p_row < a.n_rows && a.mask[p_row] == 0) p_row += n_clusters;
+        if (n_tiles == 0) p_row = a.n_rows;
+    }
+    unsigned q_cons = 0;  // tiles consumed so far (same value in every thread)
+    bool alive = true;    // false after a wait timed out: skip the ring, keep meeting barriers
+
+    auto produce = [&]() {  // thread 0: keep up to STAGES tiles in flight
+        while (alive && p_row < a.n_rows && q_prod - q_cons < static_cast<unsigned>(STAGES)) {
+            const unsigned slot = q_prod % STAGES;
+            const unsigned parity = (q_prod / STAGES) & 1u;
+            if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
+                alive = false;
+                break;
+            }
+            const int first = p_tile * TILE_CHUNKS;
+            const uint32_t bytes = static_cast<uint32_t>(min(TILE_CHUNKS, n_load - first)) * 16u;
+            const float* src = a.logits + p_row * static_cast<long long>(a.P) + 4LL * (c0 + first);
+            mbar_arrive_expect_tx(&full_bar[slot], bytes);
+            bulk_load(ring + static_cast<size_t>(slot) * TILE_CHUNKS, src, bytes, &full_bar[slot]);
+            q_prod++;
+            if (++p_tile == n_tiles) {
+                p_tile = 0;
+                p_row += n_clusters;
+                while (p_row < a.n_rows && a.mask[p_row] == 0) p_row += n_clusters;
+            }
+        }
+    };
+
+    unsigned row_parity = 0;
+#ifdef GRPO_TIMELINE
+    int tl_row = 0;
+#endif
+    for (long long row = cluster_id; row < a.n_rows; row += n_clusters) {
+        GRPO_TL(0);  // row start
+        float4* out = reinterpret_cast<float4*>(a.dlogits + row * static_cast<long long>(a.P));
+
+        if (a.mask[row] == 0) {  // uniform over the cluster: no barrier is reached
+            const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                const int c = c0 + j * THREADS + tid;
+                if (c < c1) store_stream(out + c, zero);
+            }
+            continue;
+        }
+
+        // ---- the selected logit, fetched before anything of the row is overwritten
+        int sel = 0;
+        float x_sel = 0.0f;
+        bool bad_sel = false;
+        RowScalars scalars = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (tid == 0) {
+            sel = a.selected[row];
+            if (sel < 0 || sel >= V) {  // the host layer rejects this earlier; never read out of the row
+                bad_sel = true;
+                sel = 0;
+            }
+            x_sel = a.logits[row * static_cast<long long>(a.P) + sel];
+            scalars = load_row_scalars(a, row);
+        }
+
+        // ---- ring -> registers, one stage at a time
+        float4 x[VEC];
+#pragma unroll
+        for (int k = 0; k < TILES; k++) {
+            if (k < n_tiles) {
+                if (tid == 0) produce();
+                const unsigned slot = q_cons % STAGES;
+                const unsigned parity = (q_cons / STAGES) & 1u;
+                if (alive) alive = mbar_wait(&full_bar[slot], parity);
+                const float4* stage = ring + static_cast<size_t>(slot) * TILE_CHUNKS;
+#pragma unroll
+                for (int jj = 0; jj < TJ; jj++) {
+                    const int local = k * TILE_CHUNKS + jj * THREADS + tid;
+                    if (alive && local < n_load)
+                        x[k * TJ + jj] = stage[jj * THREADS + tid];
+                    else
+                        x[k * TJ + jj] = make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[slot]);
+                q_cons++;
+            } else {
+#pragma unroll
+                for (int jj = 0; jj < TJ; jj++) x[k * TJ + jj] = make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
+            }
+        }
+        if (tid == 0) produce();  // refill the stages the last tile released
+        GRPO_TL(1);  // ring -> registers done
+
+        // ---- padding columns of the chunk that straddles V, finiteness probe, thread maximum
+        if (special_j >= 0) {  // the one thread that owns the chunk holding column V
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                if (j == special_j) {
+                    if (v_rem < 2) x[j].y = kNegInf;
+                    if (v_rem < 3) x[j].z = kNegInf;
+                    x[j].w = kNegInf;
+                }
+            }
+        }
+        float chk = 0.0f;
+        float m = kNegInf;
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            if (CHECK) {
+                // x * 0 is NaN for an infinite or NaN logit and 0 otherwise; -inf marks "no column here"
+                if (x[j].x != kNegInf) chk = fmaf(x[j].x, 0.0f, chk);
+                if (x[j].y != kNegInf) chk = fmaf(x[j].y, 0.0f, chk);
+                if (x[j].z != kNegInf) chk = fmaf(x[j].z, 0.0f, chk);
+                if (x[j].w != kNegInf) chk = fmaf(x[j].w, 0.0f, chk);
+            }
+            m = fmaxf(m, max4(x[j]));
+        }
+
+        // ---- one exp per element relative to the warp's maximum; compensated fp32 sums (two
+        //      independent Kahan chains) keep the thread's total exact to double rounding
+        const float m_warp = warp_max(m);
+        const float shift = (m_warp == kNegInf ? 0.0f : m_warp) * kLog2eHi;
+        float sa = 0.0f, ca = 0.0f, sb = 0.0f, cb = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            x[j].x = exp_rel(x[j].x, shift);
+            x[j].y = exp_rel(x[j].y, shift);
+            x[j].z = exp_rel(x[j].z, shift);
+            x[j].w = exp_rel(x[j].w, shift);
+            kahan_add(sa, ca, x[j].x);
+            kahan_add(sb, cb, x[j].y);
+            kahan_add(sa, ca, x[j].z);
+            kahan_add(sb, cb, x[j].w);
+        }
+        const double s0 = static_cast<double>(sa) - static_cast<double>(ca);
+        const double s1 = static_cast<double>(sb) - static_cast<double>(cb);
+        GRPO_TL(2);  // exp + compensated sums done
+        const double s_warp = warp_sum_all(s0 + s1);
+        if (CHECK) chk = warp_sum_f(chk);
+        if (lane == 0) {
+            warp_m[warp] = m_warp;
+            warp_shift[warp] = shift;
+            warp_s[warp] = s_warp;
+            if (CHECK) warp_chk[warp] = chk;
+        }
+        __syncthreads();
+
+        GRPO_TL(3);  // exp + sums done, past first block barrier
+        // ---- CTA combine (warp 0): factors in double, fixed shuffle trees
+        double f = 0.0;       // warp 0, lane w: scale of warp w's terms relative to e^m_cta
+        float m_cta = kNegInf;
+        if (warp == 0) {
+            const float ml = lane < WARPS ? warp_m[lane] : kNegInf;
+            m_cta = warp_max(ml);
+            double s = 0.0;
+            float c = 0.0f;
+            if (lane < WARPS && ml != kNegInf) {
+                // the warp's terms are 2^(x*log2e - shift_w); relative to e^m_cta they scale by this
+                f = exp2(static_cast<double>(warp_shift[lane]) - static_cast<double>(m_cta) * kLog2eD) * kEx2BiasFix;
+                s = warp_s[lane] * f;
+            }
+            if (CHECK && lane < WARPS) c = warp_chk[lane];
+            s = warp_sum_all(s);
+            if (CHECK) c = warp_sum_f(c);
+            if (CLUSTER > 1) {
+                if (lane == 0) {
+                    Exchange e;
+                    e.s = s;
+                    e.m = m_cta;
+                    e.chk = c;
+                    exchange[row_parity][0] = e;
+                }
+            } else {
+                if (lane < WARPS) warp_f[lane] = f;
+                if (lane == 0) {
+                    row_max_sh = m_cta;
+                    row_z_sh = s;
+                    row_chk_sh = c;
+                }
+            }
+        }
+        if (CLUSTER > 1) {
+            cg::cluster_group cluster = cg::this_cluster();
+            cluster.sync();  // every thread of every CTA: the exchange records are visible cluster-wide
+            if (warp == 0) {
+                Exchange e;
+                e.s = 0.0;
+                e.m = kNegInf;
+                e.chk = 0.0f;
+                if (lane < CLUSTER) e = *cluster.map_shared_rank(&exchange[row_parity][0], lane);
+                const float m_row = warp_max(e.m);
+                const double fr = e.m == kNegInf ? 0.0 : exp(static_cast<double>(e.m) - static_cast<double>(m_row));
+                const double z_row = warp_sum_all(e.s * fr);
+                float c = 0.0f;
+                if (CHECK) c = warp_sum_f(e.chk);
+                const double rescale =
+                    m_cta == kNegInf ? 0.0 : exp(static_cast<double>(m_cta) - static_cast<double>(m_row));
+                if (lane < WARPS) warp_f[lane] = f * rescale;
+                if (lane == 0) {
+                    row_max_sh = m_row;
+                    row_z_sh = z_row;
+                    row_chk_sh = c;
+                }
+            }
+        }
+        __syncthreads();
+
+        GRPO_TL(4);  // combine done
+        // ---- heavy elements redone in double (only rows whose normaliser is small enough to have any)
+        const float m_row = row_max_sh;
+        double z = row_z_sh;
+        const bool heavy_row = z < 1.0 / kHeavyFraction;  // uniform over the cluster
+        if (heavy_row) {
+            double delta = 0.0;
+            const double f_d = warp_f[warp];
+            const float f_f = static_cast<float>(f_d);
+            const float cut = static_cast<float>(z * kHeavyFraction * 0.999) / f_f;
+            // the thread's largest term is that of its maximum: most threads leave here
+            if (m != kNegInf && exp_rel(m, shift) * 1.001f >= cut) {
+                const float* in = a.logits + row * static_cast<long long>(a.P);
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    const int c = c0 + j * THREADS + tid;
+                    const float e4[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if (e4[q] >= cut) {
+                            const double exact = exp(static_cast<double>(in[4 * c + q]) - static_cast<double>(m_row));
+                            delta += exact - static_cast<double>(e4[q]) * f_d;
+                        }
+                    }
+                }
+            }
+            delta = warp_sum_all(delta);
+            if (lane == 0) warp_d[warp] = delta;
+            __syncthreads();
+        }
+
+        GRPO_TL(5);  // heavy phase done
+        // ---- row leader (warp 0): heavy correction, log-sum-exp, token loss.  Every CTA of the
+        //      cluster repeats it on the same bits; rank 0 records the row's terms.
+        if (CLUSTER > 1 && heavy_row) {
+            if (warp == 0) {
+                double d = lane < WARPS ? warp_d[lane] : 0.0;
+                d = warp_sum_all(d);
+                if (lane == 0) {
+                    Exchange e;
+                    e.s = d;
+                    e.m = 0.0f;
+                    e.chk = 0.0f;
+                    exchange[row_parity][1] = e;
+                }
+            }
+            cg::this_cluster().sync();
+        }
+        if (warp == 0) {
+            if (heavy_row) {
+                double d = 0.0;
+                if (CLUSTER > 1) {
+                    if (lane < CLUSTER) d = cg::this_cluster().map_shared_rank(&exchange[row_parity][1], lane)->s;
+                } else {
+                    if (lane < WARPS) d = warp_d[lane];
+                }
+                z += warp_sum_all(d);
+            }
+            if (lane == 0)
+                bc = row_leader_fast(a, row, m_row, z, x_sel, sel, scalars,
+                                     bad_sel || (CHECK && row_chk_sh != 0.0f) || !alive, crank == 0);
+        }
+        __syncthreads();
+
+        GRPO_TL(6);  // leader done
+        // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
+        const RowBroadcast b = bc;
+        const float coef = static_cast<float>(warp_f[warp]) * b.neg_g_over_z;
+        if (special_j >= 0) {  // padding columns inside the chunk that straddles V come back as +0
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                if (j == special_j) {
+                    if (v_rem < 2) x[j].y = 0.0f;
+                    if (v_rem < 3) x[j].z = 0.0f;
+                    x[j].w = 0.0f;
+                }
+            }
+        }
+        float e_sel = 0.0f;  // the selected column's term, if this thread holds it
+        const int sel_local = (b.selected >> 2) - c0;
+        const bool owns_sel = sel_local >= 0 && sel_local < c1 - c0 && sel_local % THREADS == tid;
+        if (owns_sel) {
+            const int j_sel = sel_local / THREADS, q_sel = b.selected & 3;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                if (j == j_sel) e_sel = q_sel == 0 ? x[j].x : q_sel == 1 ? x[j].y : q_sel == 2 ? x[j].z : x[j].w;
+            }
+        }
         const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
-            const int c = c0 + j * THREADS + tid;
-            if (c < c1) store_stream(out + c, zero);
+            const int local = j * THREADS + tid;
+            if (local < c1 - c0) {
+                float4 o = zero;  // columns [V, P) of the slice
+                if (local < n_load) o = make_float4(x[j].x * coef, x[j].y * coef, x[j].z * coef, x[j].w * coef);
+                store_stream(out + c0 + local, o);
+            }
         }
-        if (crank == 0 && tid == 0) {
-            a.row_terms[row] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (a.selected_logp) a.selected_logp[row] = 0.0f;
-        }
-        return;
+        // same thread, same address, program order: this store lands after the vector store above
+        if (owns_sel) a.dlogits[row * static_cast<long long>(a.P) + b.selected] = fmaf(e_sel, coef, b.g);
+        GRPO_TL(7);  // stores issued
+        row_parity ^= 1u;
     }
 
-    // ---- the selected logit, fetched before anything of the row is overwritten
-    int sel = 0;
-    float x_sel = 0.0f;
-    bool bad_sel = false;
+    // ---- shutdown: nothing may still be landing in this CTA's shared memory when it retires
     if (tid == 0) {
-        sel = a.selected[row];
-        if (sel < 0 || sel >= V) {  // host layer rejects this earlier; never read out of the row
-            bad_sel = true;
-            sel = 0;
+        while (q_cons < q_prod) {  // requested but never consumed (only after a timeout)
+            mbar_wait(&full_bar[q_cons % STAGES], (q_cons / STAGES) & 1u);
+            q_cons++;
         }
-        x_sel = a.logits[row * static_cast<long long>(a.P) + sel];
+        if (!alive) *a.status = 1;
+    } else if (!alive) {
+        *a.status = 1;
     }
-
-    // ---- one read of the row: VEC independent 128-bit loads per thread
-    float4 x[VEC];
-    const float ninf = -CUDART_INF_F;
-#pragma unroll
-    for (int j = 0; j < VEC; j++) {
-        const int c = c0 + j * THREADS + tid;
-        if (c < c1 && 4 * c < V)
-            x[j] = load_stream(in + c);
-        else
-            x[j] = make_float4(ninf, ninf, ninf, ninf);
-    }
-    float chk = 0.0f;
-    float m = ninf;
-#pragma unroll
-    for (int j = 0; j < VEC; j++) {
-        const int c = c0 + j * THREADS + tid;
-        if (4 * c + 4 > V && 4 * c < V) {  // the one chunk that straddles column V: drop the padding
-            if (4 * c + 1 >= V) x[j].y = ninf;
-            if (4 * c + 2 >= V) x[j].z = ninf;
-            if (4 * c + 3 >= V) x[j].w = ninf;
-            if (CHECK) {
-                chk = fmaf(x[j].x, 0.0f, chk);
-                if (4 * c + 1 < V) chk = fmaf(x[j].y, 0.0f, chk);
-                if (4 * c + 2 < V) chk = fmaf(x[j].z, 0.0f, chk);
-            }
-        } else if (CHECK && 4 * c < V && c < c1) {
-            // x * 0 is NaN for an infinite or NaN logit and 0 otherwise
-            chk = fmaf(x[j].x, 0.0f, chk);
-            chk = fmaf(x[j].y, 0.0f, chk);
-            chk = fmaf(x[j].z, 0.0f, chk);
-            chk = fmaf(x[j].w, 0.0f, chk);
-        }
-        m = fmaxf(m, max4(x[j]));
-    }
-
-    // ---- one exp per element, kept in the registers that held the logits
-    const float m_ref = m == ninf ? 0.0f : m;
-    const float shift = m_ref * kLog2e;
-    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-#pragma unroll
-    for (int j = 0; j < VEC; j++) {
-        x[j].x = ex2_approx(fmaf(x[j].x, kLog2e, -shift));
-        x[j].y = ex2_approx(fmaf(x[j].y, kLog2e, -shift));
-        x[j].z = ex2_approx(fmaf(x[j].z, kLog2e, -shift));
-        x[j].w = ex2_approx(fmaf(x[j].w, kLog2e, -shift));
-        s0 += x[j].x;
-        s1 += x[j].y;
-        s2 += x[j].z;
-        s3 += x[j].w;
-    }
-    RowStat st;
-    st.m = m;
-    // the thread's terms are relative to 2^shift with shift = fl(m * log2 e); fold the rounding of
-    // that product back in so that s is relative to e^m, as merge() assumes
-    const float corr = shift_correction(m_ref, shift);
-    st.s = ((s0 + s1) + (s2 + s3)) * corr;
-
-    // ---- CTA reduction: shuffles, then one shared-memory round
-    st = warp_merge(st);
-    if (CHECK) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) chk += __shfl_xor_sync(0xffffffffu, chk, o);
-    }
-    if (lane == 0) {
-        warp_stat[warp] = st;
-        if (CHECK) warp_chk[warp] = chk;
-    }
-    __syncthreads();
-
-    if (warp == 0) {
-        RowStat v;
-        v.m = ninf;
-        v.s = 0.0f;
-        float c = 0.0f;
-        if (lane < WARPS) {
-            v = warp_stat[lane];
-            if (CHECK) c = warp_chk[lane];
-        }
-        v = warp_merge(v);
-        if (CHECK) {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-        }
-        if (CLUSTER > 1) {
-            if (lane == 0) exchange = make_float4(v.m, v.s, c, 0.0f);
-        } else if (lane == 0) {
-            bc = row_leader(a, row, v, x_sel, sel, bad_sel || (CHECK && c != 0.0f), true);
-        }
-    }
-
-    if (CLUSTER > 1) {
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();  // every CTA's exchange record is visible cluster-wide
-        if (warp == 0) {
-            RowStat v;
-            v.m = ninf;
-            v.s = 0.0f;
-            float c = 0.0f;
-            if (lane < CLUSTER) {
-                const float4 e = *cluster.map_shared_rank(&exchange, lane);
-                v.m = e.x;
-                v.s = e.y;
-                c = e.z;
-            }
-            v = warp_merge(v);
-            if (CHECK) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-            }
-            // every CTA's leader repeats the same scalar math on the same bits; rank 0 records it
-            if (lane == 0) bc = row_leader(a, row, v, x_sel, sel, bad_sel || (CHECK && c != 0.0f), crank == 0);
-        }
-        cluster.barrier_arrive();  // peers may retire once everyone has read their records
-    }
-    __syncthreads();
-
-    // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
-    const RowBroadcast b = bc;
-    const float coef = ex2_approx((m_ref - b.row_max) * kLog2e) * corr * b.neg_g_over_z;
-    const int sel_chunk = b.selected >> 2, sel_lane = b.selected & 3;
-#pragma unroll
-    for (int j = 0; j < VEC; j++) {
-        const int c = c0 + j * THREADS + tid;
-        if (c < c1) {
-            float4 o;
-            if (4 * c < V) {
-                o.x = x[j].x * coef;
-                o.y = x[j].y * coef;
-                o.z = x[j].z * coef;
-                o.w = x[j].w * coef;
-                if (c == sel_chunk) {
-                    if (sel_lane == 0) o.x += b.g;
-                    if (sel_lane == 1) o.y += b.g;
-                    if (sel_lane == 2) o.z += b.g;
-                    if (sel_lane == 3) o.w += b.g;
-                }
-                if (4 * c + 4 > V) {  // padding columns inside the straddling chunk
-                    if (4 * c + 1 >= V) o.y = 0.0f;
-                    if (4 * c + 2 >= V) o.z = 0.0f;
-                    if (4 * c + 3 >= V) o.w = 0.0f;
-                }
-            } else {
-                o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            }
-            store_stream(out + c, o);
-        }
-    }
-    if (CLUSTER > 1) cg::this_cluster().barrier_wait();
+    if (CLUSTER > 1) cg::this_cluster().sync();  // peers may still be reading this CTA's exchange records
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -313,6 +607,8 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
     constexpr int WARPS = kStreamThreads / 32;
     __shared__ float red[WARPS];
     __shared__ float red_chk[WARPS];
+    __shared__ double red_d[WARPS];
+    __shared__ double z_sh;
     __shared__ RowBroadcast bc;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long row = blockIdx.x;
@@ -322,25 +618,18 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
 
     if (a.mask[row] == 0) {
         for (int v = tid; v < P; v += kStreamThreads) out[v] = 0.0f;
-        if (tid == 0) {
-            a.row_terms[row] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (a.selected_logp) a.selected_logp[row] = 0.0f;
-        }
         return;
     }
 
     // sweep 1: maximum (and the finiteness probe)
-    float m = -CUDART_INF_F, chk = 0.0f;
+    float m = kNegInf, chk = 0.0f;
     for (int v = tid; v < V; v += kStreamThreads) {
         const float x = in[v];
         m = fmaxf(m, x);
         if (CHECK) chk = fmaf(x, 0.0f, chk);
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (CHECK) chk += __shfl_xor_sync(0xffffffffu, chk, o);
-    }
+    m = warp_max(m);
+    if (CHECK) chk = warp_sum_f(chk);
     if (lane == 0) {
         red[warp] = m;
         if (CHECK) red_chk[warp] = chk;
@@ -353,50 +642,99 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
         m = fmaxf(m, red[k]);
         if (CHECK) chk += red_chk[k];
     }
-    __syncthreads();
 
-    // sweep 2: normaliser relative to the row maximum
-    const float shift = m * kLog2e;
-    float s = 0.0f;
-    for (int v = tid; v < V; v += kStreamThreads) s += ex2_approx(fmaf(in[v], kLog2e, -shift));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) red[warp] = s;
+    // sweep 2: normaliser in double; terms are 2^(x*log2e - shift), rescaled to e^m once at the end
+    const float shift = m * kLog2eHi;
+    const double f_d = exp2(static_cast<double>(shift) - static_cast<double>(m) * kLog2eD) * kEx2BiasFix;
+    double s = 0.0;
+    for (int v = tid; v < V; v += kStreamThreads) s += static_cast<double>(exp_rel(in[v], shift));
+    s = warp_sum_all(s);
+    if (lane == 0) red_d[warp] = s;
     __syncthreads();
     if (tid == 0) {
-        float z = 0.0f;
+        double z = 0.0;
 #pragma unroll
-        for (int k = 0; k < WARPS; k++) z += red[k];
+        for (int k = 0; k < WARPS; k++) z += red_d[k];
+        z_sh = z * f_d;
+    }
+    __syncthreads();
+    double z = z_sh;
+
+    // sweep 3 (rows with heavy elements only): redo those elements in double
+    if (z < 1.0 / kHeavyFraction) {
+        const float cut = static_cast<float>(z * kHeavyFraction * 0.999 / f_d);
+        double delta = 0.0;
+        for (int v = tid; v < V; v += kStreamThreads) {
+            const float x = in[v];
+            const float e = exp_rel(x, shift);
+            if (e >= cut) delta += exp(static_cast<double>(x) - static_cast<double>(m)) - static_cast<double>(e) * f_d;
+        }
+        delta = warp_sum_all(delta);
+        __syncthreads();  // red_d is reused
+        if (lane == 0) red_d[warp] = delta;
+        __syncthreads();
+        if (tid == 0) {
+            double d = 0.0;
+#pragma unroll
+            for (int k = 0; k < WARPS; k++) d += red_d[k];
+            z_sh = z + d;
+        }
+        __syncthreads();
+        z = z_sh;
+    }
+
+    if (tid == 0) {
         int sel = a.selected[row];
         bool bad = CHECK && chk != 0.0f;
         if (sel < 0 || sel >= V) {
             bad = true;
             sel = 0;
         }
-        RowStat st;
-        st.m = m;
-        st.s = z * shift_correction(m, shift);
-        bc = row_leader(a, row, st, in[sel], sel, bad, true);
+        bc = row_leader_fast(a, row, m, z, in[sel], sel, load_row_scalars(a, row), bad, true);
     }
     __syncthreads();
 
-    // sweep 3: gradient; each element is read and then overwritten by the same thread
+    // last sweep: gradient; each element is read and then overwritten by the same thread
     const RowBroadcast b = bc;
-    const float coef = b.neg_g_over_z * shift_correction(m, shift);
+    const float coef = b.neg_g_over_z * static_cast<float>(f_d);
     for (int v = tid; v < V; v += kStreamThreads) {
-        const float e = ex2_approx(fmaf(in[v], kLog2e, -shift));
+        const float e = exp_rel(in[v], shift);
         out[v] = e * coef + (v == b.selected ? b.g : 0.0f);
     }
     for (int v = V + tid; v < P; v += kStreamThreads) out[v] = 0.0f;
 }
 
-// One block sums the per-row terms in a fixed order (double accumulators).
-__global__ void __launch_bounds__(1024) logits_finalize_kernel(const float4* __restrict__ terms, long long n_rows,
+// Terms kernel: one thread per row redoes the row's scalar step in double -- log-sum-exp,
+// log p(selected) rounded to fp32 exactly as the reference rounds it, the two exponentials --
+// and leaves {w*loss, w*pg, w*kl, flags} in the first 16 bytes of the row's record.
+__global__ void __launch_bounds__(128) logits_terms_kernel(const LogitsArgs a) {
+    const long long row = static_cast<long long>(blockIdx.x) * 128 + threadIdx.x;
+    if (row >= a.n_rows) return;
+    float4 out = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float lp_new = 0.0f;
+    if (a.mask[row] != 0) {
+        const RowRecord r = a.rows[row];
+        const RowScalars sc = load_row_scalars(a, row);
+        const double lse = static_cast<double>(r.m) + log(r.z);
+        lp_new = static_cast<float>(static_cast<double>(r.x_sel) - lse);
+        const TokenTerms t = token_terms<true>(lp_new, sc.lp_old, sc.lp_ref, sc.adv, sc.w, a.clip_eps, a.beta);
+        float flags = r.flags;
+        if (!finite_f(t.grad) || !finite_f(t.grad / static_cast<float>(r.z))) flags += kRowBadGrad;
+        out = make_float4(t.loss, t.pg, t.kl, flags);
+    }
+    *reinterpret_cast<float4*>(a.rows + row) = out;
+    if (a.selected_logp) a.selected_logp[row] = lp_new;
+}
+
+// One block sums the per-row terms in a fixed order (double accumulators).  A non-zero status
+// word (a pipeline wait timed out) turns the record's bad_inputs negative.
+__global__ void __launch_bounds__(1024) logits_finalize_kernel(const RowRecord* __restrict__ rows, long long n_rows,
+                                                               const int* __restrict__ status,
                                                                grpo_b200_result_t* result) {
     __shared__ double scratch[5 * 1024 / 32];
     double v[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
     for (long long r = threadIdx.x; r < n_rows; r += 1024) {
-        const float4 t = terms[r];
+        const float4 t = *reinterpret_cast<const float4*>(rows + r);
         v[0] += static_cast<double>(t.x);
         v[1] += static_cast<double>(t.y);
         v[2] += static_cast<double>(t.z);
@@ -410,49 +748,50 @@ __global__ void __launch_bounds__(1024) logits_finalize_kernel(const float4* __r
         result->pg_loss = v[1];
         result->kl = v[2];
         result->bad_grads = v[3];
-        result->bad_inputs = v[4];
+        result->bad_inputs = *status != 0 ? -1.0 : v[4];
     }
 }
 
-// ---- variant table of the row-resident kernel ---------------------------------------------------
+// ---- variant table of the pipelined kernel --------------------------------------------------------
 struct Variant {
-    int cluster, threads, vec;
+    int cluster, threads, vec, tj, stages;
     const char* name;
 };
 
-// Capacity of a variant in floats: cluster * threads * vec * 4.
+// Capacity of a variant in floats: cluster * threads * vec * 4.  Name: cluster x threads x vec.
 constexpr Variant kVariants[] = {
-    {1, 256, 8, "1x256x8"},    // 0:  <=   8192
-    {2, 256, 8, "2x256x8"},    // 1:  <=  16384
-    {4, 256, 8, "4x256x8"},    // 2:  <=  32768
-    {8, 256, 8, "8x256x8"},    // 3:  <=  65536
-    {8, 512, 8, "8x512x8"},    // 4:  <= 131072
-    {16, 256, 8, "16x256x8"},  // 5:  <= 131072 (non-portable cluster size)
-    {2, 512, 8, "2x512x8"},    // 6:  <=  32768
-    {1, 1024, 8, "1x1024x8"},  // 7:  <=  32768
-    {4, 512, 8, "4x512x8"},    // 8:  <=  65536
-    {2, 1024, 8, "2x1024x8"},  // 9:  <=  65536
-    {4, 1024, 8, "4x1024x8"},  // 10: <= 131072
-    {8, 128, 8, "8x128x8"},    // 11: <=  32768
-    {8, 256, 4, "8x256x4"},    // 12: <=  32768
-    {16, 256, 4, "16x256x4"},  // 13: <=  65536
-    {4, 512, 4, "4x512x4"},    // 14: <=  32768
-    {1, 128, 2, "1x128x2"},    // 15: <=   1024
-    {16, 512, 4, "16x512x4"},  // 16: <= 131072
+    {1, 1024, 8, 2, 6, "1x1024x8"},   // 0:  <=  32768  one CTA per SM, 192 KB ring
+    {2, 1024, 8, 2, 6, "2x1024x8"},   // 1:  <=  65536
+    {4, 1024, 8, 2, 6, "4x1024x8"},   // 2:  <= 131072
+    {8, 1024, 8, 2, 6, "8x1024x8"},   // 3:  <= 262144
+    {1, 512, 16, 4, 6, "1x512x16"},   // 4:  <=  32768  fewer, fatter threads
+    {2, 512, 16, 4, 6, "2x512x16"},   // 5:  <=  65536
+    {4, 512, 16, 4, 6, "4x512x16"},   // 6:  <= 131072
+    {1, 256, 8, 2, 6, "1x256x8"},     // 7:  <=   8192  48 KB ring, several CTAs per SM
+    {1, 512, 8, 2, 6, "1x512x8"},     // 8:  <=  16384  96 KB ring, two CTAs per SM
+    {2, 512, 8, 2, 6, "2x512x8"},     // 9:  <=  32768  two CTAs per SM from different clusters
+    {4, 512, 8, 2, 6, "4x512x8"},     // 10: <=  65536
+    {8, 512, 8, 2, 6, "8x512x8"},     // 11: <= 131072
+    {1, 1024, 8, 1, 12, "1x1024x8s"}, // 12: <=  32768  16 KB stages
+    {2, 1024, 8, 1, 12, "2x1024x8s"}, // 13: <=  65536
+    {4, 1024, 8, 1, 12, "4x1024x8s"}, // 14: <= 131072
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
-template <int THREADS, int VEC, int CLUSTER, bool CHECK>
+template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, bool CHECK>
 cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
-    auto kernel = logits_resident_kernel<THREADS, VEC, CLUSTER, CHECK>;
-    if (CLUSTER > 8) {
-        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        if (err != cudaSuccess) return err;
-    }
+    auto kernel = logits_pipelined_kernel<THREADS, VEC, TJ, STAGES, CLUSTER, CHECK>;
+    constexpr size_t ring_bytes = static_cast<size_t>(STAGES) * TJ * THREADS * sizeof(float4);
+    // per device: opt in to the large dynamic shared memory and find how many clusters fit at once
+    static int clusters_cached[64] = {0};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(a.n_rows * CLUSTER), 1, 1);
     cfg.blockDim = dim3(THREADS, 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = ring_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -461,29 +800,51 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = CLUSTER > 1 ? 1 : 0;
+
+    int max_clusters = clusters_cached[dev];
+    if (max_clusters == 0) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_bytes));
+        if (err != cudaSuccess) return err;
+        int sms = 0;
+        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return err;
+        if (CLUSTER == 1) {
+            // plain launch: every SM takes CTAs independently
+            int per_sm = 0;
+            err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, ring_bytes);
+            if (err != cudaSuccess) return err;
+            max_clusters = per_sm * sms;
+        } else {
+            cfg.gridDim = dim3(static_cast<unsigned>(sms / CLUSTER * CLUSTER * 4), 1, 1);
+            err = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+            if (err != cudaSuccess) return err;
+        }
+        if (max_clusters < 1) return cudaErrorLaunchOutOfResources;
+        clusters_cached[dev] = max_clusters;
+    }
+    const long long clusters = a.n_rows < max_clusters ? a.n_rows : max_clusters;
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * CLUSTER), 1, 1);
     return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
 template <bool CHECK>
 cudaError_t launch_by_index(int variant, const LogitsArgs& a, cudaStream_t stream) {
     switch (variant) {
-        case 0: return launch_variant<256, 8, 1, CHECK>(a, stream);
-        case 1: return launch_variant<256, 8, 2, CHECK>(a, stream);
-        case 2: return launch_variant<256, 8, 4, CHECK>(a, stream);
-        case 3: return launch_variant<256, 8, 8, CHECK>(a, stream);
-        case 4: return launch_variant<512, 8, 8, CHECK>(a, stream);
-        case 5: return launch_variant<256, 8, 16, CHECK>(a, stream);
-        case 6: return launch_variant<512, 8, 2, CHECK>(a, stream);
-        case 7: return launch_variant<1024, 8, 1, CHECK>(a, stream);
-        case 8: return launch_variant<512, 8, 4, CHECK>(a, stream);
-        case 9: return launch_variant<1024, 8, 2, CHECK>(a, stream);
-        case 10: return launch_variant<1024, 8, 4, CHECK>(a, stream);
-        case 11: return launch_variant<128, 8, 8, CHECK>(a, stream);
-        case 12: return launch_variant<256, 4, 8, CHECK>(a, stream);
-        case 13: return launch_variant<256, 4, 16, CHECK>(a, stream);
-        case 14: return launch_variant<512, 4, 4, CHECK>(a, stream);
-        case 15: return launch_variant<128, 2, 1, CHECK>(a, stream);
-        case 16: return launch_variant<512, 4, 16, CHECK>(a, stream);
+        case 0: return launch_variant<1024, 8, 2, 6, 1, CHECK>(a, stream);
+        case 1: return launch_variant<1024, 8, 2, 6, 2, CHECK>(a, stream);
+        case 2: return launch_variant<1024, 8, 2, 6, 4, CHECK>(a, stream);
+        case 3: return launch_variant<1024, 8, 2, 6, 8, CHECK>(a, stream);
+        case 4: return launch_variant<512, 16, 4, 6, 1, CHECK>(a, stream);
+        case 5: return launch_variant<512, 16, 4, 6, 2, CHECK>(a, stream);
+        case 6: return launch_variant<512, 16, 4, 6, 4, CHECK>(a, stream);
+        case 7: return launch_variant<256, 8, 2, 6, 1, CHECK>(a, stream);
+        case 8: return launch_variant<512, 8, 2, 6, 1, CHECK>(a, stream);
+        case 9: return launch_variant<512, 8, 2, 6, 2, CHECK>(a, stream);
+        case 10: return launch_variant<512, 8, 2, 6, 4, CHECK>(a, stream);
+        case 11: return launch_variant<512, 8, 2, 6, 8, CHECK>(a, stream);
+        case 12: return launch_variant<1024, 8, 1, 12, 1, CHECK>(a, stream);
+        case 13: return launch_variant<1024, 8, 1, 12, 2, CHECK>(a, stream);
+        case 14: return launch_variant<1024, 8, 1, 12, 4, CHECK>(a, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -496,6 +857,12 @@ bool variant_fits(int variant, int P) {
 }
 
 }  // namespace
+
+#ifdef GRPO_TIMELINE
+extern "C" int grpo_b200_debug_timeline(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(g_timeline)) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 int resident_variant_count() { return kNumVariants; }
 
@@ -510,8 +877,7 @@ int pick_resident_variant(const void* logits, const void* dlogits, int V, int P)
     if ((reinterpret_cast<uintptr_t>(logits) & 15u) || (reinterpret_cast<uintptr_t>(dlogits) & 15u)) return -1;
     if (g_forced_variant >= 0 && g_forced_variant < kNumVariants)
         return variant_fits(g_forced_variant, P) ? g_forced_variant : -1;
-    // smallest cluster that holds the row with 256-thread CTAs of 8 chunks per thread
-    static const int order[] = {15, 0, 1, 2, 3, 4};
+    static const int order[] = {7, 8, 0, 1, 2, 3};  // smallest configuration that holds the row
     for (int idx : order)
         if (variant_fits(idx, P)) return idx;
     return -1;
@@ -530,8 +896,14 @@ cudaError_t launch_logits_streaming(bool check, const LogitsArgs& a, cudaStream_
     return cudaGetLastError();
 }
 
+cudaError_t launch_logits_terms(const LogitsArgs& a, cudaStream_t stream) {
+    const unsigned blocks = static_cast<unsigned>((a.n_rows + 127) / 128);
+    logits_terms_kernel<<<blocks, 128, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_logits_finalize(const LogitsArgs& a, cudaStream_t stream) {
-    logits_finalize_kernel<<<1, 1024, 0, stream>>>(a.row_terms, a.n_rows, a.result);
+    logits_finalize_kernel<<<1, 1024, 0, stream>>>(a.rows, a.n_rows, a.status, a.result);
     return cudaGetLastError();
 }
 

@@ -137,7 +137,7 @@ def test_every_resident_variant_matches_oracle():
     names = D.variants()
     try:
         for idx, name in enumerate(names):
-            c, t, v = (int(x) for x in name.split("x"))
+            c, t, v = (int("".join(ch for ch in x if ch.isdigit())) for x in name.split("x"))
             cap = c * t * v * 4
             V = cap - 37 if cap > 2048 else cap - 5
             P = cap
@@ -293,8 +293,8 @@ def test_gpt2_shaped_config_at_full_size():
                                                  adv_h[sample // T], np.ones(k, np.int32), 1, k, 1, V,
                                                  0.2, 0.01, W.TOKEN_MEAN, 0.0)
     got = x[torch.from_numpy(sample).cuda()].cpu().numpy()[:, :V]
-    scale = np.float64(k) / np.float64(n_valid)
-    assert_grad(got, d_s.astype(np.float64) * scale, "sampled rows of the GPT-2-shaped batch")
+    scale = np.float64(n_valid) / np.float64(k)  # compare at the oracle's 1/48 weight, where 1e-7 absolute bites
+    assert_grad(got.astype(np.float64) * scale, d_s, "sampled rows of the GPT-2-shaped batch")
 
 
 def test_reference_driver_against_this_library():

@@ -146,9 +146,12 @@ def test_device_layer_offsets_and_unaligned():
     assert (lengths.cpu().numpy() == b.mask.reshape(b.S, b.T).sum(1)).all()
     weights, meta = D.weights_from_lengths(lengths, b.reduction, b.length_alpha)
     assert meta.tolist() == [int(b.mask.sum()), 0]
-    L = b.mask.reshape(b.S, b.T).sum(1).astype(np.float32)
-    w_np = (np.power(L, np.float32(b.length_alpha) - np.float32(1.0)) / np.float32(b.S)).astype(np.float32)
-    assert (weights.cpu().numpy().view(np.uint32) == w_np.view(np.uint32)).all()
+    # the reference's weights, read off its own gradient: with all log-probabilities 0 and A = 1 each
+    # active token's dlogp is exactly -weight (src/cpu/grpo_loss.cpp:124-131,160)
+    z = np.zeros(b.N, np.float32)
+    w_ref = -oracle().loss(z, z, z, np.ones(b.S, np.float32), b.mask, b.B, b.G, b.T, 0.2, 0.0, b.reduction,
+                           b.length_alpha)[2].reshape(b.S, b.T)[:, 0]
+    assert (weights.cpu().numpy().view(np.uint32) == w_ref.view(np.uint32)).all()
     adv = t(b.advantages)
     # whole batch
     dlogp, res = D.loss(t(b.logp_new), t(b.logp_old), t(b.logp_ref), adv, weights, mask, b.T, b.clip_eps, b.beta)
