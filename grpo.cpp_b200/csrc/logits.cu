@@ -97,12 +97,25 @@ __device__ __forceinline__ double warp_sum_all(double v) {
     return v;
 }
 
-// Kahan step: (s, c) += v with the rounding error of each addition carried in c; the running
-// total is s - c.  Plain fp32 adds, never re-associated by the compiler without fast-math.
-__device__ __forceinline__ void kahan_add(float& s, float& c, float v) {
-    const float y = __fsub_rn(v, c);
-    const float t = __fadd_rn(s, y);
-    c = __fsub_rn(__fsub_rn(t, s), y);
+// Packed fp32x2 arithmetic (sm_100): one instruction works on two independent lanes, each with
+// IEEE round-to-nearest, so the hot loops below issue half as many FMA-pipe instructions.
+__device__ __forceinline__ float2 lo2(float4 v) { return make_float2(v.x, v.y); }
+__device__ __forceinline__ float2 hi2(float4 v) { return make_float2(v.z, v.w); }
+
+// e = 2^(x*log2e - shift) on a pair
+__device__ __forceinline__ float2 exp_rel2(float2 x, float2 neg_shift) {
+    const float2 t = __ffma2_rn(x, make_float2(kLog2eLo, kLog2eLo), __ffma2_rn(x, make_float2(kLog2eHi, kLog2eHi), neg_shift));
+    return make_float2(ex2_approx(t.x), ex2_approx(t.y));
+}
+
+// Kahan step on a pair of independent chains.  nc holds MINUS the running compensation, so that
+// every operation is a packed add or a packed multiply-add by -1:
+//   y = v - c;  t = s + y;  c' = (t - s) - y  <=>  nc' = (s - t) + y
+__device__ __forceinline__ void kahan_add2(float2& s, float2& nc, float2 v) {
+    const float2 y = __fadd2_rn(v, nc);
+    const float2 t = __fadd2_rn(s, y);
+    const float2 d = __ffma2_rn(t, make_float2(-1.0f, -1.0f), s);
+    nc = __fadd2_rn(d, y);
     s = t;
 }
 
@@ -183,6 +196,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
+// Non-blocking probe of a phase (try_wait may suspend the thread for a while; test_wait never does).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
 // Bounded wait: gives up after about two seconds of SM clock and reports failure, so a lost
 // copy can never hang the device.  The caller then stops touching the ring ("not alive") but
 // keeps meeting every block and cluster barrier until the kernel ends.
@@ -202,22 +227,120 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  : "memory");
 }
 
+// exp(d) in double for d in about [-40, 0.5], to ~1e-11 relative: 2^k * exp(r) with r = d - k ln2
+// (two-constant reduction) and a degree-10 Taylor polynomial.  A dozen dependent double
+// operations instead of the library routine's several dozen: this sits on a row's serial path.
+__device__ __forceinline__ double exp_small_d(double d) {
+    const double kf = rint(d * kLog2eD);
+    double r = fma(-kf, 6.93147180369123816490e-01, d);
+    r = fma(-kf, 1.90821492927058770002e-10, r);
+    double p = 1.0 / 3628800.0;
+    p = fma(p, r, 1.0 / 362880.0);
+    p = fma(p, r, 1.0 / 40320.0);
+    p = fma(p, r, 1.0 / 5040.0);
+    p = fma(p, r, 1.0 / 720.0);
+    p = fma(p, r, 1.0 / 120.0);
+    p = fma(p, r, 1.0 / 24.0);
+    p = fma(p, r, 1.0 / 6.0);
+    p = fma(p, r, 0.5);
+    p = fma(p, r, 1.0);
+    p = fma(p, r, 1.0);
+    const int k = static_cast<int>(kf);
+    return p * __hiloint2double((1023 + k) << 20, 0);
+}
+
+// Correction for one heavy term given its logit: exact exp(x - row_max) minus the fp32 term as it
+// entered the sum (the same deterministic function as in the main sweep, so the same bits).
+__device__ __forceinline__ double heavy_term(float xv, float shift, float cut, float row_max, double f_d) {
+    const float e = exp_rel(xv, shift);
+    if (xv == kNegInf || e < cut) return 0.0;
+    return exp_small_d(static_cast<double>(xv) - static_cast<double>(row_max)) - static_cast<double>(e) * f_d;
+}
+
 // Per-CTA partial of the row reduction, exchanged through distributed shared memory.
-struct Exchange {
-    double s;   // normaliser of the CTA's slice relative to e^m
-    float m;    // maximum of the slice (-inf when empty)
-    float chk;  // finiteness probe
+struct __align__(16) Exchange {
+    double s;     // normaliser of the CTA's slice relative to e^m (round 0) / heavy correction (round 1)
+    float m;      // maximum of the slice (-inf when empty)
+    float chk;    // finiteness probe
+    float x_sel;  // the selected logit, if this CTA's slice holds it
+    int has_sel;
 };
+
+// barrier 1: the consumer warps only (the producer warp never joins it)
+__device__ __forceinline__ void consumer_sync(int threads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+// arrive (release, cluster scope) on the mbarrier that sits at the same shared-memory offset in
+// CTA `rank` of this cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, unsigned rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(bar)), "r"(rank));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if (clock64() - start > (1LL << 32)) return false;
+    }
+    return true;
+}
+
+// One round of the cluster-wide exchange, run by warp 0 of every CTA of the cluster: lane p
+// pushes this CTA's record into CTA p's inbox and arrives on CTA p's mbarrier; then the warp
+// waits until all CLUSTER records have landed in its own inbox and lane r returns CTA r's.
+// Only the leader warps take part: no cluster-wide hardware barrier, nobody else waits.
+template <int CLUSTER>
+__device__ __forceinline__ Exchange cluster_exchange(Exchange mine, Exchange* inbox, uint64_t* bar, unsigned& uses,
+                                                     int lane, unsigned crank, bool& alive) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (lane < CLUSTER) {
+        *cluster.map_shared_rank(inbox + crank, lane) = mine;
+        mbar_arrive_remote(bar, lane);
+    }
+    if (alive) alive = mbar_wait_cluster(bar, uses & 1u);
+    uses++;
+    Exchange e;
+    e.s = 0.0;
+    e.m = kNegInf;
+    e.chk = 0.0f;
+    e.x_sel = 0.0f;
+    e.has_sel = 0;
+    if (lane < CLUSTER) e = inbox[lane];
+    return e;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Pipelined kernel.  Requires P % 4 == 0 and 16-byte aligned bases; the dispatcher guarantees
 // ceil(P/4 / CLUSTER) <= THREADS * VEC.  TJ chunks per thread per ring stage, STAGES stages.
+// The block has THREADS consumer threads plus one producer warp.
+//
+// Nothing on a row's critical path is an ordinary global load: such a load queues behind the
+// bulk copies this SM already has in flight and comes back thousands of cycles later.  The
+// per-row scalars are staged per batch of rows, the selected logit is read back from the ring,
+// and the elements that are redone in double are the thread's own two largest chunk maxima.
+// Issuing a bulk copy can itself stall for a long time when the copy queue is full, which is
+// why a dedicated warp does it.
 // ---------------------------------------------------------------------------------------------
 template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, bool CHECK>
-__global__ void __launch_bounds__(THREADS, (VEC >= 16 ? 512 : 1024) / THREADS) logits_pipelined_kernel(const LogitsArgs a) {
+__global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : 2)
+    logits_pipelined_kernel(const LogitsArgs a) {
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE_CHUNKS = TJ * THREADS;
     constexpr int TILES = VEC / TJ;
+    constexpr int BATCH = 256;  // rows whose scalars are staged at once
     static_assert(VEC % TJ == 0, "tiles must cover the per-thread chunks exactly");
     static_assert(WARPS <= 32 && CLUSTER <= 32, "one lane per warp / per cluster rank in the combine step");
 
@@ -225,39 +348,50 @@ __global__ void __launch_bounds__(THREADS, (VEC >= 16 ? 512 : 1024) / THREADS) l
     float4* ring = reinterpret_cast<float4*>(ring_raw);
     __shared__ uint64_t full_bar[STAGES];
     __shared__ uint64_t empty_bar[STAGES];
+    __shared__ uint64_t xbar[2][2];                 // [row parity][round]: CLUSTER arrivals each
+    __shared__ Exchange inbox[2][2][CLUSTER];       // [row parity][round][source rank]
     __shared__ float warp_m[WARPS];
     __shared__ float warp_shift[WARPS];
     __shared__ float warp_chk[WARPS];
     __shared__ double warp_s[WARPS];
     __shared__ double warp_f[WARPS];  // 2^(shift_w - M*log2e): the warp's terms relative to the row maximum
     __shared__ double warp_d[WARPS];
-    __shared__ Exchange exchange[2][2];  // [row parity][reduction round]
     __shared__ float row_max_sh;
     __shared__ double row_z_sh;
     __shared__ float row_chk_sh;
     __shared__ RowBroadcast bc;
+    __shared__ int meta_sel[BATCH];
+    __shared__ float meta_old[BATCH];
+    __shared__ float meta_ref[BATCH];
+    __shared__ float meta_adv[BATCH];
+    __shared__ float meta_w[BATCH];
+    __shared__ unsigned char meta_mask[BATCH];
+    __shared__ unsigned q_cons_final;
+    __shared__ int abort_sh;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
+    const bool is_producer = warp == WARPS;
     unsigned crank = 0;
     if (CLUSTER > 1) crank = cg::this_cluster().block_rank();
-    const long long cluster_id = blockIdx.x / CLUSTER;
-    const long long n_clusters = gridDim.x / CLUSTER;
+    const int cluster_id = blockIdx.x / CLUSTER;
+    const int n_clusters = gridDim.x / CLUSTER;
+    const int n_rows = static_cast<int>(a.n_rows);  // the C ABI caps rows at INT_MAX
 
     const int V = a.V;
     const int P4 = a.P >> 2;
     const int per_cta = (P4 + CLUSTER - 1) / CLUSTER;
-    const int c0 = crank * per_cta;                          // first chunk of this CTA's slice
-    const int c1 = min(c0 + per_cta, P4);                    // end of the slice (stores)
-    const int n_load = max(min(c1, (V + 3) >> 2) - c0, 0);   // chunks that hold vocabulary (loads)
+    const int c0 = static_cast<int>(crank) * per_cta;        // first chunk of this CTA's slice
+    const int n_store = max(min(c0 + per_cta, P4) - c0, 0);  // chunks of the slice (stores)
+    const int n_load = max(min(c0 + n_store, (V + 3) >> 2) - c0, 0);  // chunks that hold vocabulary (loads)
     const int n_tiles = (n_load + TILE_CHUNKS - 1) / TILE_CHUNKS;
     // The single chunk that straddles column V (when V % 4 != 0) belongs to one thread of one CTA:
     // special_j is its register index there, -1 everywhere else.
     const int v_rem = V & 3;
     int special_j = -1;
-    if (v_rem != 0) {
+    if (v_rem != 0 && !is_producer) {
         const int cs = (V >> 2) - c0;
-        if (cs >= 0 && cs < c1 - c0 && cs % THREADS == tid) special_j = cs / THREADS;
+        if (cs >= 0 && cs < n_store && cs % THREADS == tid) special_j = cs / THREADS;
     }
 
     if (tid == 0) {
@@ -266,335 +400,354 @@ __global__ void __launch_bounds__(THREADS, (VEC >= 16 ? 512 : 1024) / THREADS) l
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], WARPS);
         }
+        for (int i = 0; i < 4; i++) mbar_init(&xbar[i >> 1][i & 1], CLUSTER);
+        q_cons_final = 0;
+        abort_sh = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    if (CLUSTER > 1) cg::this_cluster().sync();  // peers' barriers exist before anyone arrives on them remotely
 
-    // producer cursor (meaningful in thread 0 only): next tile to request
-    long long p_row = cluster_id;
-    int p_tile = 0;
-    unsigned q_prod = 0;
-    if (tid == 0) {
-        while (p_row < a.n_rows && a.mask[p_row] == 0) p_row += n_clusters;
-        if (n_tiles == 0) p_row = a.n_rows;
-    }
-    unsigned q_cons = 0;  // tiles consumed so far (same value in every thread)
-    bool alive = true;    // false after a wait timed out: skip the ring, keep meeting barriers
+    // Rows of this cluster: cluster_id + k * n_clusters, k = 0 .. n_mine-1, walked in batches.
+    const int n_mine = cluster_id < n_rows ? (n_rows - cluster_id + n_clusters - 1) / n_clusters : 0;
 
-    auto produce = [&]() {  // thread 0: keep up to STAGES tiles in flight
-        while (alive && p_row < a.n_rows && q_prod - q_cons < static_cast<unsigned>(STAGES)) {
-            const unsigned slot = q_prod % STAGES;
-            const unsigned parity = (q_prod / STAGES) & 1u;
-            if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
-                alive = false;
-                break;
-            }
-            const int first = p_tile * TILE_CHUNKS;
-            const uint32_t bytes = static_cast<uint32_t>(min(TILE_CHUNKS, n_load - first)) * 16u;
-            const float* src = a.logits + p_row * static_cast<long long>(a.P) + 4LL * (c0 + first);
-            mbar_arrive_expect_tx(&full_bar[slot], bytes);
-            bulk_load(ring + static_cast<size_t>(slot) * TILE_CHUNKS, src, bytes, &full_bar[slot]);
-            q_prod++;
-            if (++p_tile == n_tiles) {
-                p_tile = 0;
-                p_row += n_clusters;
-                while (p_row < a.n_rows && a.mask[p_row] == 0) p_row += n_clusters;
-            }
-        }
-    };
-
+    unsigned q = 0;     // consumers: tiles consumed; producer: tiles requested
+    bool alive = true;  // false after a wait timed out: skip the ring, keep meeting barriers
     unsigned row_parity = 0;
+    unsigned xuses[2][2] = {{0u, 0u}, {0u, 0u}};
 #ifdef GRPO_TIMELINE
     int tl_row = 0;
 #endif
-    for (long long row = cluster_id; row < a.n_rows; row += n_clusters) {
-        GRPO_TL(0);  // row start
-        float4* out = reinterpret_cast<float4*>(a.dlogits + row * static_cast<long long>(a.P));
 
-        if (a.mask[row] == 0) {  // uniform over the cluster: no barrier is reached
-            const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-            for (int j = 0; j < VEC; j++) {
-                const int c = c0 + j * THREADS + tid;
-                if (c < c1) store_stream(out + c, zero);
+    for (int batch_first = 0; batch_first < n_mine; batch_first += BATCH) {
+        const int batch_rows = min(BATCH, n_mine - batch_first);
+        __syncthreads();  // everyone, producer included, is done with the previous batch's scalars
+        for (int i = tid; i < batch_rows; i += THREADS + 32) {
+            const size_t r = static_cast<size_t>(cluster_id) + static_cast<size_t>(batch_first + i) * n_clusters;
+            const int mk = a.mask[r];
+            meta_mask[i] = mk != 0;
+            if (mk != 0) {
+                const long long seq = (a.row_offset + static_cast<long long>(r)) / a.tokens_per_seq;
+                meta_sel[i] = a.selected[r];
+                meta_old[i] = a.logp_old[r];
+                meta_ref[i] = a.logp_ref[r];
+                meta_adv[i] = a.advantages[seq];
+                meta_w[i] = a.weights[seq];
             }
-            continue;
-        }
-
-        // ---- the selected logit, fetched before anything of the row is overwritten
-        int sel = 0;
-        float x_sel = 0.0f;
-        bool bad_sel = false;
-        RowScalars scalars = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (tid == 0) {
-            sel = a.selected[row];
-            if (sel < 0 || sel >= V) {  // the host layer rejects this earlier; never read out of the row
-                bad_sel = true;
-                sel = 0;
-            }
-            x_sel = a.logits[row * static_cast<long long>(a.P) + sel];
-            scalars = load_row_scalars(a, row);
-        }
-
-        // ---- ring -> registers, one stage at a time
-        float4 x[VEC];
-#pragma unroll
-        for (int k = 0; k < TILES; k++) {
-            if (k < n_tiles) {
-                if (tid == 0) produce();
-                const unsigned slot = q_cons % STAGES;
-                const unsigned parity = (q_cons / STAGES) & 1u;
-                if (alive) alive = mbar_wait(&full_bar[slot], parity);
-                const float4* stage = ring + static_cast<size_t>(slot) * TILE_CHUNKS;
-#pragma unroll
-                for (int jj = 0; jj < TJ; jj++) {
-                    const int local = k * TILE_CHUNKS + jj * THREADS + tid;
-                    if (alive && local < n_load)
-                        x[k * TJ + jj] = stage[jj * THREADS + tid];
-                    else
-                        x[k * TJ + jj] = make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty_bar[slot]);
-                q_cons++;
-            } else {
-#pragma unroll
-                for (int jj = 0; jj < TJ; jj++) x[k * TJ + jj] = make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
-            }
-        }
-        if (tid == 0) produce();  // refill the stages the last tile released
-        GRPO_TL(1);  // ring -> registers done
-
-        // ---- padding columns of the chunk that straddles V, finiteness probe, thread maximum
-        if (special_j >= 0) {  // the one thread that owns the chunk holding column V
-#pragma unroll
-            for (int j = 0; j < VEC; j++) {
-                if (j == special_j) {
-                    if (v_rem < 2) x[j].y = kNegInf;
-                    if (v_rem < 3) x[j].z = kNegInf;
-                    x[j].w = kNegInf;
-                }
-            }
-        }
-        float chk = 0.0f;
-        float m = kNegInf;
-#pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            if (CHECK) {
-                // x * 0 is NaN for an infinite or NaN logit and 0 otherwise; -inf marks "no column here"
-                if (x[j].x != kNegInf) chk = fmaf(x[j].x, 0.0f, chk);
-                if (x[j].y != kNegInf) chk = fmaf(x[j].y, 0.0f, chk);
-                if (x[j].z != kNegInf) chk = fmaf(x[j].z, 0.0f, chk);
-                if (x[j].w != kNegInf) chk = fmaf(x[j].w, 0.0f, chk);
-            }
-            m = fmaxf(m, max4(x[j]));
-        }
-
-        // ---- one exp per element relative to the warp's maximum; compensated fp32 sums (two
-        //      independent Kahan chains) keep the thread's total exact to double rounding
-        const float m_warp = warp_max(m);
-        const float shift = (m_warp == kNegInf ? 0.0f : m_warp) * kLog2eHi;
-        float sa = 0.0f, ca = 0.0f, sb = 0.0f, cb = 0.0f;
-#pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            x[j].x = exp_rel(x[j].x, shift);
-            x[j].y = exp_rel(x[j].y, shift);
-            x[j].z = exp_rel(x[j].z, shift);
-            x[j].w = exp_rel(x[j].w, shift);
-            kahan_add(sa, ca, x[j].x);
-            kahan_add(sb, cb, x[j].y);
-            kahan_add(sa, ca, x[j].z);
-            kahan_add(sb, cb, x[j].w);
-        }
-        const double s0 = static_cast<double>(sa) - static_cast<double>(ca);
-        const double s1 = static_cast<double>(sb) - static_cast<double>(cb);
-        GRPO_TL(2);  // exp + compensated sums done
-        const double s_warp = warp_sum_all(s0 + s1);
-        if (CHECK) chk = warp_sum_f(chk);
-        if (lane == 0) {
-            warp_m[warp] = m_warp;
-            warp_shift[warp] = shift;
-            warp_s[warp] = s_warp;
-            if (CHECK) warp_chk[warp] = chk;
         }
         __syncthreads();
 
-        GRPO_TL(3);  // exp + sums done, past first block barrier
-        // ---- CTA combine (warp 0): factors in double, fixed shuffle trees
-        double f = 0.0;       // warp 0, lane w: scale of warp w's terms relative to e^m_cta
-        float m_cta = kNegInf;
-        if (warp == 0) {
-            const float ml = lane < WARPS ? warp_m[lane] : kNegInf;
-            m_cta = warp_max(ml);
-            double s = 0.0;
-            float c = 0.0f;
-            if (lane < WARPS && ml != kNegInf) {
-                // the warp's terms are 2^(x*log2e - shift_w); relative to e^m_cta they scale by this
-                f = exp2(static_cast<double>(warp_shift[lane]) - static_cast<double>(m_cta) * kLog2eD) * kEx2BiasFix;
-                s = warp_s[lane] * f;
-            }
-            if (CHECK && lane < WARPS) c = warp_chk[lane];
-            s = warp_sum_all(s);
-            if (CHECK) c = warp_sum_f(c);
-            if (CLUSTER > 1) {
-                if (lane == 0) {
-                    Exchange e;
-                    e.s = s;
-                    e.m = m_cta;
-                    e.chk = c;
-                    exchange[row_parity][0] = e;
-                }
-            } else {
-                if (lane < WARPS) warp_f[lane] = f;
-                if (lane == 0) {
-                    row_max_sh = m_cta;
-                    row_z_sh = s;
-                    row_chk_sh = c;
+        if (is_producer) {
+            // ---- producer warp: one lane requests every tile of every active row of the batch, in
+            //      order, as the ring's stages come free
+            if (lane == 0 && n_tiles > 0) {
+                for (int k_row = 0; k_row < batch_rows && alive; k_row++) {
+                    if (meta_mask[k_row] == 0) continue;
+                    const size_t p_row =
+                        static_cast<size_t>(cluster_id) + static_cast<size_t>(batch_first + k_row) * n_clusters;
+                    const float* row_src = a.logits + p_row * static_cast<size_t>(a.P) + 4 * static_cast<size_t>(c0);
+                    for (int t = 0; t < n_tiles; t++) {
+                        const unsigned slot = q % STAGES;
+                        const unsigned parity = (q / STAGES) & 1u;
+                        if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
+                            alive = false;
+                            abort_sh = 1;
+                            break;
+                        }
+                        const int first = t * TILE_CHUNKS;
+                        const uint32_t bytes = static_cast<uint32_t>(min(TILE_CHUNKS, n_load - first)) * 16u;
+                        mbar_arrive_expect_tx(&full_bar[slot], bytes);
+                        bulk_load(ring + static_cast<size_t>(slot) * TILE_CHUNKS, row_src + 4 * static_cast<size_t>(first),
+                                  bytes, &full_bar[slot]);
+                        q++;
+                    }
                 }
             }
+            continue;  // next batch
         }
-        if (CLUSTER > 1) {
-            cg::cluster_group cluster = cg::this_cluster();
-            cluster.sync();  // every thread of every CTA: the exchange records are visible cluster-wide
+
+        // ---- consumer warps
+        for (int k_row = 0; k_row < batch_rows; k_row++) {
+            const size_t row = static_cast<size_t>(cluster_id) + static_cast<size_t>(batch_first + k_row) * n_clusters;
+            GRPO_TL(0);  // row start
+            float4* out = reinterpret_cast<float4*>(a.dlogits + row * static_cast<size_t>(a.P)) + c0;
+
+            if (meta_mask[k_row] == 0) {  // uniform over the cluster: no barrier is reached
+                const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    const int local = j * THREADS + tid;
+                    if (local < n_store) store_stream(out + local, zero);
+                }
+                continue;
+            }
+
+            // ---- ring -> registers, one stage at a time
+            const int slot0 = static_cast<int>(q % STAGES);
+            float4 x[VEC];
+#pragma unroll
+            for (int k = 0; k < TILES; k++) {
+                if (k < n_tiles) {
+                    const unsigned slot = q % STAGES;
+                    const unsigned parity = (q / STAGES) & 1u;
+                    if (alive) alive = mbar_wait(&full_bar[slot], parity);
+                    const float4* stage = ring + static_cast<size_t>(slot) * TILE_CHUNKS;
+#pragma unroll
+                    for (int jj = 0; jj < TJ; jj++) {
+                        const int local = k * TILE_CHUNKS + jj * THREADS + tid;
+                        if (alive && local < n_load)
+                            x[k * TJ + jj] = stage[jj * THREADS + tid];
+                        else
+                            x[k * TJ + jj] = make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
+                    }
+                    q++;
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < TJ; jj++) x[k * TJ + jj] = make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
+                }
+            }
+            GRPO_TL(1);  // ring -> registers done
+
+            // ---- the selected logit, read back from the stage that holds its chunk
+            int sel = 0;
+            float x_sel = 0.0f;
+            int has_sel = 0;
+            bool bad_sel = false;
+            if (tid == 0) {
+                sel = meta_sel[k_row];
+                if (sel < 0 || sel >= V) {  // the host layer rejects this earlier; never read out of the row
+                    bad_sel = true;
+                    sel = 0;
+                }
+                const int sc = (sel >> 2) - c0;
+                if (alive && sc >= 0 && sc < n_load) {
+                    int slot = slot0 + sc / TILE_CHUNKS;
+                    if (slot >= STAGES) slot -= STAGES;
+                    const float* stage = reinterpret_cast<const float*>(ring + static_cast<size_t>(slot) * TILE_CHUNKS);
+                    x_sel = stage[4 * (sc % TILE_CHUNKS) + (sel & 3)];
+                    has_sel = 1;
+                }
+            }
+
+            // ---- the row's stages go back to the producer; the next rows' tiles start streaming now
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < TILES; k++) {
+                    if (k < n_tiles) {
+                        int slot = slot0 + k;
+                        if (slot >= STAGES) slot -= STAGES;
+                        mbar_arrive(&empty_bar[slot]);
+                    }
+                }
+            }
+
+            // ---- padding columns of the chunk that straddles V, finiteness probe, and the thread's
+            //      two largest chunk maxima (its candidates for the double-precision correction)
+            if (special_j >= 0) {  // the one thread that owns the chunk holding column V
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    if (j == special_j) {
+                        if (v_rem < 2) x[j].y = kNegInf;
+                        if (v_rem < 3) x[j].z = kNegInf;
+                        x[j].w = kNegInf;
+                    }
+                }
+            }
+            float chk = 0.0f;
+            float m = kNegInf, m2 = kNegInf;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                if (CHECK) {
+                    // x * 0 is NaN for an infinite or NaN logit and 0 otherwise; -inf marks "no column here"
+                    if (x[j].x != kNegInf) chk = fmaf(x[j].x, 0.0f, chk);
+                    if (x[j].y != kNegInf) chk = fmaf(x[j].y, 0.0f, chk);
+                    if (x[j].z != kNegInf) chk = fmaf(x[j].z, 0.0f, chk);
+                    if (x[j].w != kNegInf) chk = fmaf(x[j].w, 0.0f, chk);
+                }
+                const float cm = max4(x[j]);
+                m2 = fmaxf(m2, fminf(m, cm));
+                m = fmaxf(m, cm);
+            }
+
+            // ---- one exp per element relative to the warp's maximum; compensated fp32 sums (four
+            //      independent Kahan chains, two per packed instruction) keep the thread's total
+            //      exact to double rounding
+            const float m_warp = warp_max(m);
+            const float shift = (m_warp == kNegInf ? 0.0f : m_warp) * kLog2eHi;
+            const float2 neg_shift2 = make_float2(-shift, -shift);
+            float2 sa = make_float2(0.0f, 0.0f), nca = sa, sb = sa, ncb = sa;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                const float2 ea = exp_rel2(lo2(x[j]), neg_shift2);
+                const float2 eb = exp_rel2(hi2(x[j]), neg_shift2);
+                x[j] = make_float4(ea.x, ea.y, eb.x, eb.y);
+                kahan_add2(sa, nca, ea);
+                kahan_add2(sb, ncb, eb);
+            }
+            const double s_thread = ((static_cast<double>(sa.x) + static_cast<double>(nca.x)) +
+                                     (static_cast<double>(sa.y) + static_cast<double>(nca.y))) +
+                                    ((static_cast<double>(sb.x) + static_cast<double>(ncb.x)) +
+                                     (static_cast<double>(sb.y) + static_cast<double>(ncb.y)));
+            GRPO_TL(2);  // exp + compensated sums done
+            const double s_warp = warp_sum_all(s_thread);
+            if (CHECK) chk = warp_sum_f(chk);
+            if (lane == 0) {
+                warp_m[warp] = m_warp;
+                warp_shift[warp] = shift;
+                warp_s[warp] = s_warp;
+                if (CHECK) warp_chk[warp] = chk;
+            }
+            consumer_sync(THREADS);
+            GRPO_TL(3);  // past the first block barrier
+
+            // ---- CTA combine, then cluster exchange (warp 0): factors in double, fixed shuffle trees
             if (warp == 0) {
-                Exchange e;
-                e.s = 0.0;
-                e.m = kNegInf;
-                e.chk = 0.0f;
-                if (lane < CLUSTER) e = *cluster.map_shared_rank(&exchange[row_parity][0], lane);
-                const float m_row = warp_max(e.m);
-                const double fr = e.m == kNegInf ? 0.0 : exp(static_cast<double>(e.m) - static_cast<double>(m_row));
-                const double z_row = warp_sum_all(e.s * fr);
+                const float ml = lane < WARPS ? warp_m[lane] : kNegInf;
+                const float m_cta = warp_max(ml);
+                double f = 0.0, s = 0.0;  // lane w: scale of warp w's terms relative to e^m_cta
                 float c = 0.0f;
-                if (CHECK) c = warp_sum_f(e.chk);
-                const double rescale =
-                    m_cta == kNegInf ? 0.0 : exp(static_cast<double>(m_cta) - static_cast<double>(m_row));
-                if (lane < WARPS) warp_f[lane] = f * rescale;
+                if (lane < WARPS && ml != kNegInf) {
+                    // the warp's terms are 2^(x*log2e - shift_w); relative to e^m_cta they scale by this
+                    f = exp2(static_cast<double>(warp_shift[lane]) - static_cast<double>(m_cta) * kLog2eD) * kEx2BiasFix;
+                    s = warp_s[lane] * f;
+                }
+                if (CHECK && lane < WARPS) c = warp_chk[lane];
+                s = warp_sum_all(s);
+                if (CHECK) c = warp_sum_f(c);
+                float m_row = m_cta;
+                double z_row = s;
+                if (CLUSTER > 1) {
+                    Exchange mine;
+                    mine.s = s;
+                    mine.m = m_cta;
+                    mine.chk = c;
+                    mine.x_sel = __shfl_sync(0xffffffffu, x_sel, 0);
+                    mine.has_sel = __shfl_sync(0xffffffffu, has_sel, 0);
+                    const Exchange e = cluster_exchange<CLUSTER>(mine, inbox[row_parity][0], &xbar[row_parity][0],
+                                                                 xuses[row_parity][0], lane, crank, alive);
+                    m_row = warp_max(e.m);
+                    const double fr = e.m == kNegInf ? 0.0 : exp(static_cast<double>(e.m) - static_cast<double>(m_row));
+                    z_row = warp_sum_all(e.s * fr);
+                    if (CHECK) c = warp_sum_f(e.chk);
+                    x_sel = warp_sum_f(e.has_sel ? e.x_sel : 0.0f);  // exactly one CTA holds the selected column
+                    f *= m_cta == kNegInf ? 0.0 : exp(static_cast<double>(m_cta) - static_cast<double>(m_row));
+                }
+                if (lane < WARPS) warp_f[lane] = f;
                 if (lane == 0) {
                     row_max_sh = m_row;
                     row_z_sh = z_row;
                     row_chk_sh = c;
                 }
             }
-        }
-        __syncthreads();
+            consumer_sync(THREADS);
+            GRPO_TL(4);  // combine done
 
-        GRPO_TL(4);  // combine done
-        // ---- heavy elements redone in double (only rows whose normaliser is small enough to have any)
-        const float m_row = row_max_sh;
-        double z = row_z_sh;
-        const bool heavy_row = z < 1.0 / kHeavyFraction;  // uniform over the cluster
-        if (heavy_row) {
-            double delta = 0.0;
-            const double f_d = warp_f[warp];
-            const float f_f = static_cast<float>(f_d);
-            const float cut = static_cast<float>(z * kHeavyFraction * 0.999) / f_f;
-            // the thread's largest term is that of its maximum: most threads leave here
-            if (m != kNegInf && exp_rel(m, shift) * 1.001f >= cut) {
-                const float* in = a.logits + row * static_cast<long long>(a.P);
+            // ---- heavy terms redone in double (only rows whose normaliser is small enough to have any)
+            const float m_row = row_max_sh;
+            double z = row_z_sh;
+            const bool heavy_row = z < 1.0 / kHeavyFraction;  // uniform over the cluster
+            if (heavy_row) {
+                double delta = 0.0;
+                const double f_d = warp_f[warp];
+                const float f_f = static_cast<float>(f_d);
+                const float cut = static_cast<float>(z * kHeavyFraction * 0.999) / f_f;
+                // The thread's largest term is that of its maximum: most threads leave here.  Its two
+                // largest chunk maxima are corrected; a third heavy term in one thread, or two in one
+                // chunk, would keep its fp32 error (~1e-7 of a term that weighs a few 1/256 of the sum).
+                if (m != kNegInf && exp_rel(m, shift) * 1.001f >= cut)
+                    delta = heavy_term(m, shift, cut, m_row, f_d) + heavy_term(m2, shift, cut, m_row, f_d);
+                delta = warp_sum_all(delta);
+                if (lane == 0) warp_d[warp] = delta;
+                consumer_sync(THREADS);
+            }
+            GRPO_TL(5);  // heavy phase done
+
+            // ---- row leader (warp 0): heavy correction, then dlogp.  Every CTA of the cluster repeats
+            //      it on the same bits; rank 0 writes the row's record.
+            if (warp == 0) {
+                if (heavy_row) {
+                    double d = lane < WARPS ? warp_d[lane] : 0.0;
+                    d = warp_sum_all(d);
+                    if (CLUSTER > 1) {
+                        Exchange mine;
+                        mine.s = d;
+                        mine.m = 0.0f;
+                        mine.chk = 0.0f;
+                        mine.x_sel = 0.0f;
+                        mine.has_sel = 0;
+                        const Exchange e = cluster_exchange<CLUSTER>(mine, inbox[row_parity][1], &xbar[row_parity][1],
+                                                                     xuses[row_parity][1], lane, crank, alive);
+                        d = warp_sum_all(lane < CLUSTER ? e.s : 0.0);
+                    }
+                    z += d;
+                }
+                if (lane == 0)
+                    bc = row_leader_fast(a, static_cast<long long>(row), m_row, z, x_sel, sel,
+                                         RowScalars{meta_old[k_row], meta_ref[k_row], meta_adv[k_row], meta_w[k_row]},
+                                         bad_sel || (CHECK && row_chk_sh != 0.0f) || !alive, crank == 0);
+            }
+            consumer_sync(THREADS);
+            GRPO_TL(6);  // leader done
+
+            // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
+            const RowBroadcast b = bc;
+            const float coef = static_cast<float>(warp_f[warp]) * b.neg_g_over_z;
+            if (special_j >= 0) {  // padding columns inside the chunk that straddles V come back as +0
 #pragma unroll
                 for (int j = 0; j < VEC; j++) {
-                    const int c = c0 + j * THREADS + tid;
-                    const float e4[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        if (e4[q] >= cut) {
-                            const double exact = exp(static_cast<double>(in[4 * c + q]) - static_cast<double>(m_row));
-                            delta += exact - static_cast<double>(e4[q]) * f_d;
-                        }
+                    if (j == special_j) {
+                        if (v_rem < 2) x[j].y = 0.0f;
+                        if (v_rem < 3) x[j].z = 0.0f;
+                        x[j].w = 0.0f;
                     }
                 }
             }
-            delta = warp_sum_all(delta);
-            if (lane == 0) warp_d[warp] = delta;
-            __syncthreads();
-        }
-
-        GRPO_TL(5);  // heavy phase done
-        // ---- row leader (warp 0): heavy correction, log-sum-exp, token loss.  Every CTA of the
-        //      cluster repeats it on the same bits; rank 0 records the row's terms.
-        if (CLUSTER > 1 && heavy_row) {
-            if (warp == 0) {
-                double d = lane < WARPS ? warp_d[lane] : 0.0;
-                d = warp_sum_all(d);
-                if (lane == 0) {
-                    Exchange e;
-                    e.s = d;
-                    e.m = 0.0f;
-                    e.chk = 0.0f;
-                    exchange[row_parity][1] = e;
+            float e_sel = 0.0f;  // the selected column's term, if this thread holds it
+            const int sel_local = (b.selected >> 2) - c0;
+            const bool owns_sel = sel_local >= 0 && sel_local < n_load && sel_local % THREADS == tid;
+            if (owns_sel) {
+                const int j_sel = sel_local / THREADS, q_sel = b.selected & 3;
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    if (j == j_sel) e_sel = q_sel == 0 ? x[j].x : q_sel == 1 ? x[j].y : q_sel == 2 ? x[j].z : x[j].w;
                 }
             }
-            cg::this_cluster().sync();
-        }
-        if (warp == 0) {
-            if (heavy_row) {
-                double d = 0.0;
-                if (CLUSTER > 1) {
-                    if (lane < CLUSTER) d = cg::this_cluster().map_shared_rank(&exchange[row_parity][1], lane)->s;
-                } else {
-                    if (lane < WARPS) d = warp_d[lane];
-                }
-                z += warp_sum_all(d);
-            }
-            if (lane == 0)
-                bc = row_leader_fast(a, row, m_row, z, x_sel, sel, scalars,
-                                     bad_sel || (CHECK && row_chk_sh != 0.0f) || !alive, crank == 0);
-        }
-        __syncthreads();
-
-        GRPO_TL(6);  // leader done
-        // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
-        const RowBroadcast b = bc;
-        const float coef = static_cast<float>(warp_f[warp]) * b.neg_g_over_z;
-        if (special_j >= 0) {  // padding columns inside the chunk that straddles V come back as +0
+            const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float2 coef2 = make_float2(coef, coef);
 #pragma unroll
             for (int j = 0; j < VEC; j++) {
-                if (j == special_j) {
-                    if (v_rem < 2) x[j].y = 0.0f;
-                    if (v_rem < 3) x[j].z = 0.0f;
-                    x[j].w = 0.0f;
+                const int local = j * THREADS + tid;
+                if (local < n_store) {
+                    float4 o = zero;  // columns [V, P) of the slice
+                    if (local < n_load) {
+                        const float2 oa = __fmul2_rn(lo2(x[j]), coef2), ob = __fmul2_rn(hi2(x[j]), coef2);
+                        o = make_float4(oa.x, oa.y, ob.x, ob.y);
+                    }
+                    store_stream(out + local, o);
                 }
             }
-        }
-        float e_sel = 0.0f;  // the selected column's term, if this thread holds it
-        const int sel_local = (b.selected >> 2) - c0;
-        const bool owns_sel = sel_local >= 0 && sel_local < c1 - c0 && sel_local % THREADS == tid;
-        if (owns_sel) {
-            const int j_sel = sel_local / THREADS, q_sel = b.selected & 3;
-#pragma unroll
-            for (int j = 0; j < VEC; j++) {
-                if (j == j_sel) e_sel = q_sel == 0 ? x[j].x : q_sel == 1 ? x[j].y : q_sel == 2 ? x[j].z : x[j].w;
-            }
-        }
-        const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            const int local = j * THREADS + tid;
-            if (local < c1 - c0) {
-                float4 o = zero;  // columns [V, P) of the slice
-                if (local < n_load) o = make_float4(x[j].x * coef, x[j].y * coef, x[j].z * coef, x[j].w * coef);
-                store_stream(out + c0 + local, o);
-            }
-        }
-        // same thread, same address, program order: this store lands after the vector store above
-        if (owns_sel) a.dlogits[row * static_cast<long long>(a.P) + b.selected] = fmaf(e_sel, coef, b.g);
-        GRPO_TL(7);  // stores issued
-        row_parity ^= 1u;
-    }
+            // same thread, same address, program order: this store lands after the vector store above
+            if (owns_sel) a.dlogits[row * static_cast<size_t>(a.P) + b.selected] = fmaf(e_sel, coef, b.g);
+            GRPO_TL(7);  // stores issued
+            row_parity ^= 1u;
+        }  // rows of the batch
+    }      // batches
 
     // ---- shutdown: nothing may still be landing in this CTA's shared memory when it retires
-    if (tid == 0) {
-        while (q_cons < q_prod) {  // requested but never consumed (only after a timeout)
-            mbar_wait(&full_bar[q_cons % STAGES], (q_cons / STAGES) & 1u);
-            q_cons++;
+    if (tid == 0) q_cons_final = q;
+    if (!alive) abort_sh = 1;
+    __syncthreads();
+    if (is_producer && lane == 0) {
+        unsigned qc = q_cons_final;
+        while (qc < q) {  // requested but never consumed (only after a timeout)
+            mbar_wait(&full_bar[qc % STAGES], (qc / STAGES) & 1u);
+            qc++;
         }
-        if (!alive) *a.status = 1;
-    } else if (!alive) {
-        *a.status = 1;
+        if (abort_sh != 0) *a.status = 1;
     }
-    if (CLUSTER > 1) cg::this_cluster().sync();  // peers may still be reading this CTA's exchange records
+    if (CLUSTER > 1) cg::this_cluster().sync();  // no CTA retires while a peer may still push into its inbox
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -760,21 +913,21 @@ struct Variant {
 
 // Capacity of a variant in floats: cluster * threads * vec * 4.  Name: cluster x threads x vec.
 constexpr Variant kVariants[] = {
-    {1, 1024, 8, 2, 6, "1x1024x8"},   // 0:  <=  32768  one CTA per SM, 192 KB ring
-    {2, 1024, 8, 2, 6, "2x1024x8"},   // 1:  <=  65536
-    {4, 1024, 8, 2, 6, "4x1024x8"},   // 2:  <= 131072
-    {8, 1024, 8, 2, 6, "8x1024x8"},   // 3:  <= 262144
-    {1, 512, 16, 4, 6, "1x512x16"},   // 4:  <=  32768  fewer, fatter threads
-    {2, 512, 16, 4, 6, "2x512x16"},   // 5:  <=  65536
-    {4, 512, 16, 4, 6, "4x512x16"},   // 6:  <= 131072
-    {1, 256, 8, 2, 6, "1x256x8"},     // 7:  <=   8192  48 KB ring, several CTAs per SM
-    {1, 512, 8, 2, 6, "1x512x8"},     // 8:  <=  16384  96 KB ring, two CTAs per SM
-    {2, 512, 8, 2, 6, "2x512x8"},     // 9:  <=  32768  two CTAs per SM from different clusters
+    {1, 512, 16, 4, 6, "1x512x16"},   // 0:  <=  32768  one CTA per SM, 192 KB ring of 32 KB stages
+    {2, 512, 16, 4, 6, "2x512x16"},   // 1:  <=  65536
+    {4, 512, 16, 4, 6, "4x512x16"},   // 2:  <= 131072
+    {8, 512, 16, 4, 6, "8x512x16"},   // 3:  <= 262144
+    {1, 256, 16, 4, 6, "1x256x16"},   // 4:  <=  16384  96 KB ring, two CTAs per SM
+    {2, 256, 16, 4, 6, "2x256x16"},   // 5:  <=  32768
+    {4, 256, 16, 4, 6, "4x256x16"},   // 6:  <=  65536
+    {8, 256, 16, 4, 6, "8x256x16"},   // 7:  <= 131072
+    {1, 512, 8, 2, 6, "1x512x8"},     // 8:  <=  16384  96 KB ring, two CTAs per SM, 64 registers
+    {2, 512, 8, 2, 6, "2x512x8"},     // 9:  <=  32768
     {4, 512, 8, 2, 6, "4x512x8"},     // 10: <=  65536
     {8, 512, 8, 2, 6, "8x512x8"},     // 11: <= 131072
-    {1, 1024, 8, 1, 12, "1x1024x8s"}, // 12: <=  32768  16 KB stages
-    {2, 1024, 8, 1, 12, "2x1024x8s"}, // 13: <=  65536
-    {4, 1024, 8, 1, 12, "4x1024x8s"}, // 14: <= 131072
+    {1, 512, 16, 2, 12, "1x512x16s"}, // 12: <=  32768  16 KB stages
+    {2, 512, 16, 2, 12, "2x512x16s"}, // 13: <=  65536
+    {1, 128, 16, 4, 6, "1x128x16"},   // 14: <=   8192  48 KB ring, four CTAs per SM
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -790,7 +943,7 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
 
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.blockDim = dim3(THREADS + 32, 1, 1);
     cfg.dynamicSmemBytes = ring_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -811,7 +964,7 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
         if (CLUSTER == 1) {
             // plain launch: every SM takes CTAs independently
             int per_sm = 0;
-            err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, ring_bytes);
+            err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS + 32, ring_bytes);
             if (err != cudaSuccess) return err;
             max_clusters = per_sm * sms;
         } else {
@@ -830,21 +983,21 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
 template <bool CHECK>
 cudaError_t launch_by_index(int variant, const LogitsArgs& a, cudaStream_t stream) {
     switch (variant) {
-        case 0: return launch_variant<1024, 8, 2, 6, 1, CHECK>(a, stream);
-        case 1: return launch_variant<1024, 8, 2, 6, 2, CHECK>(a, stream);
-        case 2: return launch_variant<1024, 8, 2, 6, 4, CHECK>(a, stream);
-        case 3: return launch_variant<1024, 8, 2, 6, 8, CHECK>(a, stream);
-        case 4: return launch_variant<512, 16, 4, 6, 1, CHECK>(a, stream);
-        case 5: return launch_variant<512, 16, 4, 6, 2, CHECK>(a, stream);
-        case 6: return launch_variant<512, 16, 4, 6, 4, CHECK>(a, stream);
-        case 7: return launch_variant<256, 8, 2, 6, 1, CHECK>(a, stream);
+        case 0: return launch_variant<512, 16, 4, 6, 1, CHECK>(a, stream);
+        case 1: return launch_variant<512, 16, 4, 6, 2, CHECK>(a, stream);
+        case 2: return launch_variant<512, 16, 4, 6, 4, CHECK>(a, stream);
+        case 3: return launch_variant<512, 16, 4, 6, 8, CHECK>(a, stream);
+        case 4: return launch_variant<256, 16, 4, 6, 1, CHECK>(a, stream);
+        case 5: return launch_variant<256, 16, 4, 6, 2, CHECK>(a, stream);
+        case 6: return launch_variant<256, 16, 4, 6, 4, CHECK>(a, stream);
+        case 7: return launch_variant<256, 16, 4, 6, 8, CHECK>(a, stream);
         case 8: return launch_variant<512, 8, 2, 6, 1, CHECK>(a, stream);
         case 9: return launch_variant<512, 8, 2, 6, 2, CHECK>(a, stream);
         case 10: return launch_variant<512, 8, 2, 6, 4, CHECK>(a, stream);
         case 11: return launch_variant<512, 8, 2, 6, 8, CHECK>(a, stream);
-        case 12: return launch_variant<1024, 8, 1, 12, 1, CHECK>(a, stream);
-        case 13: return launch_variant<1024, 8, 1, 12, 2, CHECK>(a, stream);
-        case 14: return launch_variant<1024, 8, 1, 12, 4, CHECK>(a, stream);
+        case 12: return launch_variant<512, 16, 2, 12, 1, CHECK>(a, stream);
+        case 13: return launch_variant<512, 16, 2, 12, 2, CHECK>(a, stream);
+        case 14: return launch_variant<128, 16, 4, 6, 1, CHECK>(a, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -877,7 +1030,7 @@ int pick_resident_variant(const void* logits, const void* dlogits, int V, int P)
     if ((reinterpret_cast<uintptr_t>(logits) & 15u) || (reinterpret_cast<uintptr_t>(dlogits) & 15u)) return -1;
     if (g_forced_variant >= 0 && g_forced_variant < kNumVariants)
         return variant_fits(g_forced_variant, P) ? g_forced_variant : -1;
-    static const int order[] = {7, 8, 0, 1, 2, 3};  // smallest configuration that holds the row
+    static const int order[] = {14, 4, 0, 1, 2, 3};  // smallest configuration that holds the row
     for (int idx : order)
         if (variant_fits(idx, P)) return idx;
     return -1;
