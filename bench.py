@@ -373,7 +373,7 @@ def gpu_arm(args, spec: dict) -> None:
                     "d2h_bytes_per_step": 48, "ms_per_step": 1e3 * e2e_total / args.steps,
                     "api": "grpo_logits_cuda_device_inplace (host metadata, device logits)" if world == 1 else
                            "ShardedBoundary.prepare+step+stats from pinned host metadata"},
-            "gpu_launches": 4 * args.steps * world,
+            "gpu_launches": 5 * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_kind}",
                          "kernel": f"logits_resident_kernel<{plan}> + finalize", "ms_per_launch": k_ms,

@@ -196,18 +196,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Non-blocking probe of a phase (try_wait may suspend the thread for a while; test_wait never does).
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    return done != 0;
-}
 // Bounded wait: gives up after about two seconds of SM clock and reports failure, so a lost
 // copy can never hang the device.  The caller then stops touching the ring ("not alive") but
 // keeps meeting every block and cluster barrier until the kernel ends.
@@ -227,34 +215,33 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  : "memory");
 }
 
-// exp(d) in double for d in about [-40, 0.5], to ~1e-11 relative: 2^k * exp(r) with r = d - k ln2
-// (two-constant reduction) and a degree-10 Taylor polynomial.  A dozen dependent double
-// operations instead of the library routine's several dozen: this sits on a row's serial path.
-__device__ __forceinline__ double exp_small_d(double d) {
-    const double kf = rint(d * kLog2eD);
-    double r = fma(-kf, 6.93147180369123816490e-01, d);
-    r = fma(-kf, 1.90821492927058770002e-10, r);
-    double p = 1.0 / 3628800.0;
-    p = fma(p, r, 1.0 / 362880.0);
-    p = fma(p, r, 1.0 / 40320.0);
-    p = fma(p, r, 1.0 / 5040.0);
-    p = fma(p, r, 1.0 / 720.0);
-    p = fma(p, r, 1.0 / 120.0);
-    p = fma(p, r, 1.0 / 24.0);
-    p = fma(p, r, 1.0 / 6.0);
-    p = fma(p, r, 0.5);
+// 2^t in double for t in about [-60, 1], to ~3e-10 relative: 2^k * 2^r with r = t - k in [-1/2, 1/2]
+// and a degree-8 polynomial in r (Taylor coefficients of exp(r ln 2)).  About a dozen dependent
+// double operations instead of the library routine's several dozen: this sits on every thread's
+// path once or twice per row.
+__device__ __forceinline__ double exp2_small_d(double t) {
+    const double kf = rint(t);
+    const double r = t - kf;
+    double p = 1.3215486790144309e-06;   // ln2^8 / 8!
+    p = fma(p, r, 1.5252733804059841e-05);  // ln2^7 / 7!
+    p = fma(p, r, 1.5403530393381609e-04);  // ln2^6 / 6!
+    p = fma(p, r, 1.3333558146428443e-03);  // ln2^5 / 5!
+    p = fma(p, r, 9.6181291076284772e-03);  // ln2^4 / 4!
+    p = fma(p, r, 5.5504108664821580e-02);  // ln2^3 / 3!
+    p = fma(p, r, 2.4022650695910071e-01);  // ln2^2 / 2!
+    p = fma(p, r, 6.9314718055994531e-01);  // ln2
     p = fma(p, r, 1.0);
-    p = fma(p, r, 1.0);
-    const int k = static_cast<int>(kf);
-    return p * __hiloint2double((1023 + k) << 20, 0);
+    return p * __hiloint2double((1023 + static_cast<int>(kf)) << 20, 0);
 }
 
-// Correction for one heavy term given its logit: exact exp(x - row_max) minus the fp32 term as it
-// entered the sum (the same deterministic function as in the main sweep, so the same bits).
-__device__ __forceinline__ double heavy_term(float xv, float shift, float cut, float row_max, double f_d) {
-    const float e = exp_rel(xv, shift);
-    if (xv == kNegInf || e < cut) return 0.0;
-    return exp_small_d(static_cast<double>(xv) - static_cast<double>(row_max)) - static_cast<double>(e) * f_d;
+// Double-precision correction of one term given its logit: what 2^(x*log2e - shift) is exactly,
+// minus the fp32 term as it entered the sum (the same deterministic function as in the main
+// sweep, so the same bits).  The exact value is divided by the ex2 bias factor because the whole
+// fp32 sum is multiplied by that factor later.
+__device__ __forceinline__ double term_correction(float xv, float shift) {
+    if (xv == kNegInf) return 0.0;
+    const double exact = exp2_small_d(fma(static_cast<double>(xv), kLog2eD, -static_cast<double>(shift)));
+    return exact * (1.0 / kEx2BiasFix) - static_cast<double>(exp_rel(xv, shift));
 }
 
 // Per-CTA partial of the row reduction, exchanged through distributed shared memory.
@@ -335,7 +322,7 @@ __device__ __forceinline__ Exchange cluster_exchange(Exchange mine, Exchange* in
 // why a dedicated warp does it.
 // ---------------------------------------------------------------------------------------------
 template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, bool CHECK>
-__global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : 2)
+__global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (THREADS * VEC >= 4096 ? 2 : 4))
     logits_pipelined_kernel(const LogitsArgs a) {
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE_CHUNKS = TJ * THREADS;
@@ -355,10 +342,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : 2)
     __shared__ float warp_chk[WARPS];
     __shared__ double warp_s[WARPS];
     __shared__ double warp_f[WARPS];  // 2^(shift_w - M*log2e): the warp's terms relative to the row maximum
-    __shared__ double warp_d[WARPS];
-    __shared__ float row_max_sh;
-    __shared__ double row_z_sh;
-    __shared__ float row_chk_sh;
     __shared__ RowBroadcast bc;
     __shared__ int meta_sel[BATCH];
     __shared__ float meta_old[BATCH];
@@ -590,8 +573,12 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : 2)
                                      (static_cast<double>(sa.y) + static_cast<double>(nca.y))) +
                                     ((static_cast<double>(sb.x) + static_cast<double>(ncb.x)) +
                                      (static_cast<double>(sb.y) + static_cast<double>(ncb.y)));
+            // Every thread redoes its two largest chunk maxima in double: a row's few dominant terms
+            // are among them, and those are the terms whose fp32 error (~1e-7 each) the
+            // log-sum-exp cannot absorb.  Everything else is light enough to average out.
+            const double s_fixed = s_thread + (term_correction(m, shift) + term_correction(m2, shift));
             GRPO_TL(2);  // exp + compensated sums done
-            const double s_warp = warp_sum_all(s_thread);
+            const double s_warp = warp_sum_all(s_fixed);
             if (CHECK) chk = warp_sum_f(chk);
             if (lane == 0) {
                 warp_m[warp] = m_warp;
@@ -635,62 +622,18 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : 2)
                     f *= m_cta == kNegInf ? 0.0 : exp(static_cast<double>(m_cta) - static_cast<double>(m_row));
                 }
                 if (lane < WARPS) warp_f[lane] = f;
-                if (lane == 0) {
-                    row_max_sh = m_row;
-                    row_z_sh = z_row;
-                    row_chk_sh = c;
-                }
-            }
-            consumer_sync(THREADS);
-            GRPO_TL(4);  // combine done
-
-            // ---- heavy terms redone in double (only rows whose normaliser is small enough to have any)
-            const float m_row = row_max_sh;
-            double z = row_z_sh;
-            const bool heavy_row = z < 1.0 / kHeavyFraction;  // uniform over the cluster
-            if (heavy_row) {
-                double delta = 0.0;
-                const double f_d = warp_f[warp];
-                const float f_f = static_cast<float>(f_d);
-                const float cut = static_cast<float>(z * kHeavyFraction * 0.999) / f_f;
-                // The thread's largest term is that of its maximum: most threads leave here.  Its two
-                // largest chunk maxima are corrected; a third heavy term in one thread, or two in one
-                // chunk, would keep its fp32 error (~1e-7 of a term that weighs a few 1/256 of the sum).
-                if (m != kNegInf && exp_rel(m, shift) * 1.001f >= cut)
-                    delta = heavy_term(m, shift, cut, m_row, f_d) + heavy_term(m2, shift, cut, m_row, f_d);
-                delta = warp_sum_all(delta);
-                if (lane == 0) warp_d[warp] = delta;
-                consumer_sync(THREADS);
-            }
-            GRPO_TL(5);  // heavy phase done
-
-            // ---- row leader (warp 0): heavy correction, then dlogp.  Every CTA of the cluster repeats
-            //      it on the same bits; rank 0 writes the row's record.
-            if (warp == 0) {
-                if (heavy_row) {
-                    double d = lane < WARPS ? warp_d[lane] : 0.0;
-                    d = warp_sum_all(d);
-                    if (CLUSTER > 1) {
-                        Exchange mine;
-                        mine.s = d;
-                        mine.m = 0.0f;
-                        mine.chk = 0.0f;
-                        mine.x_sel = 0.0f;
-                        mine.has_sel = 0;
-                        const Exchange e = cluster_exchange<CLUSTER>(mine, inbox[row_parity][1], &xbar[row_parity][1],
-                                                                     xuses[row_parity][1], lane, crank, alive);
-                        d = warp_sum_all(lane < CLUSTER ? e.s : 0.0);
-                    }
-                    z += d;
-                }
+                // ---- row leader: dlogp for the backward sweep and the row's record.  Every CTA of
+                //      the cluster repeats it on the same bits; rank 0 writes the record.
                 if (lane == 0)
-                    bc = row_leader_fast(a, static_cast<long long>(row), m_row, z, x_sel, sel,
+                    bc = row_leader_fast(a, static_cast<long long>(row), m_row, z_row, x_sel, sel,
                                          RowScalars{meta_old[k_row], meta_ref[k_row], meta_adv[k_row], meta_w[k_row]},
-                                         bad_sel || (CHECK && row_chk_sh != 0.0f) || !alive, crank == 0);
+                                         bad_sel || (CHECK && c != 0.0f) || !alive, crank == 0);
             }
             consumer_sync(THREADS);
-            GRPO_TL(6);  // leader done
+            GRPO_TL(4);  // combine + leader done
 
+            GRPO_TL(5);  // (no separate correction phase)
+            GRPO_TL(6);  // leader done
             // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
             const RowBroadcast b = bc;
             const float coef = static_cast<float>(warp_f[warp]) * b.neg_g_over_z;
@@ -928,6 +871,9 @@ constexpr Variant kVariants[] = {
     {1, 512, 16, 2, 12, "1x512x16s"}, // 12: <=  32768  16 KB stages
     {2, 512, 16, 2, 12, "2x512x16s"}, // 13: <=  65536
     {1, 128, 16, 4, 6, "1x128x16"},   // 14: <=   8192  48 KB ring, four CTAs per SM
+    {2, 128, 16, 4, 6, "2x128x16"},   // 15: <=  16384
+    {4, 128, 16, 4, 6, "4x128x16"},   // 16: <=  32768
+    {8, 128, 16, 4, 6, "8x128x16"},   // 17: <=  65536
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -998,6 +944,9 @@ cudaError_t launch_by_index(int variant, const LogitsArgs& a, cudaStream_t strea
         case 12: return launch_variant<512, 16, 2, 12, 1, CHECK>(a, stream);
         case 13: return launch_variant<512, 16, 2, 12, 2, CHECK>(a, stream);
         case 14: return launch_variant<128, 16, 4, 6, 1, CHECK>(a, stream);
+        case 15: return launch_variant<128, 16, 4, 6, 2, CHECK>(a, stream);
+        case 16: return launch_variant<128, 16, 4, 6, 4, CHECK>(a, stream);
+        case 17: return launch_variant<128, 16, 4, 6, 8, CHECK>(a, stream);
         default: return cudaErrorInvalidValue;
     }
 }
