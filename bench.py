@@ -88,7 +88,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -298,11 +298,12 @@ def gpu_arm(args, spec: dict) -> None:
         e1.record()
 
     # ---- device-resident steps -------------------------------------------------------------
+    # clocks are sampled from the warm-up through the end-to-end loop: the device is busy throughout
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         restore()
         barrier()
         device_step(ev(), ev(), ev(), ev())
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     barrier()
     step_ms, kern_ms = [], []
     t_wall0 = time.perf_counter()
@@ -376,7 +377,7 @@ def gpu_arm(args, spec: dict) -> None:
             "gpu_launches": 5 * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                         "kernel": f"logits_resident_kernel<{plan}> + finalize", "ms_per_launch": k_ms,
+                         "kernel": f"logits_pipelined_kernel<{plan}> (+ terms, finalize)", "ms_per_launch": k_ms,
                          "algorithmic_bytes_per_launch": kernel_bytes, "traffic": TRAFFIC_BYTES.get(args.workload)},
         }
         if world == 1 and not args.no_cpu:
