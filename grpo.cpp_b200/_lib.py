@@ -34,6 +34,7 @@ SIGNATURES = {
     "grpo_b200_group_advantages": (_int, [_vp, _int, _int, _int, _flt, _vp, _vp, _vp]),
     "grpo_b200_loss_workspace_bytes": (_sz, [_i64]),
     "grpo_b200_loss": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _flt, _flt, _vp, _vp, _vp, _sz, _vp]),
+    "grpo_b200_loss_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _flt, _flt, _vp, _vp, _vp]),
     "grpo_b200_logits_workspace_bytes": (_sz, [_i64]),
     "grpo_b200_logits": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _flt, _flt,
                                 _int, _int, _vp, _vp, _vp, _sz, _vp]),

@@ -10,6 +10,8 @@
 //     fixed warp-order tree per block and a fixed-order pass over per-block partials: no
 //     global atomics, bit-identical results from run to run;
 //   * no accumulator memset: the finalize step overwrites the result record.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace grpo_b200 {
@@ -276,3 +278,109 @@ cudaError_t launch_group_advantages(const float* rewards, int B, int G, int mode
 }
 
 }  // namespace grpo_b200
+
+// ---------------------------------------------------------------------------------------------
+// Selected-token loss for callers that have no device memory to lend and may not allocate any.
+// ---------------------------------------------------------------------------------------------
+namespace grpo_b200 {
+namespace {
+
+constexpr long long kNoAllocMaxTokens = 1LL << 24;  // 16,777,216 tokens per call
+constexpr int kNoAllocBlocks = 1024;                // per-block partial slots held by the library
+
+// The scratch the ordinary entry point takes from its caller lives here instead: 1024 x 5 doubles
+// (40 KB) of per-block partial sums.  Every GPU that loads this library keeps the array until the
+// process exits.  In host code this name is only a handle for the runtime, not a device address.
+static __device__ __align__(256) double g_noalloc_partials[kNoAllocBlocks * kPartialWidth];
+
+std::mutex g_noalloc_mutex;
+double* g_noalloc_ptr[64] = {nullptr};  // per device: the array's device address, looked up once
+
+}  // namespace
+}  // namespace grpo_b200
+
+extern "C" int grpo_b200_loss_noalloc(const float* logp_new, const float* logp_old, const float* logp_ref,
+                                      const float* advantages, const float* weights, const int32_t* mask,
+                                      int64_t n_tokens, int64_t token_offset, int tokens_per_seq, float clip_eps,
+                                      float beta, float* dlogp, grpo_b200_result_t* result,
+                                      grpo_b200_stream_t stream) {
+    using namespace grpo_b200;
+    if (!logp_new || !logp_old || !logp_ref || !advantages || !weights || !mask || !dlogp || !result) {
+        set_error("device pointers must not be null");
+        return GRPO_B200_E_INVALID;
+    }
+    if (n_tokens <= 0 || tokens_per_seq <= 0 || token_offset < 0) {
+        set_error("B, G and T must be positive");
+        return GRPO_B200_E_INVALID;
+    }
+    if (n_tokens > kNoAllocMaxTokens) {
+        set_error("grpo_b200_loss_noalloc takes at most %lld tokens per call (got %lld); use grpo_b200_loss with a "
+                  "caller-provided workspace for larger batches",
+                  kNoAllocMaxTokens, static_cast<long long>(n_tokens));
+        return GRPO_B200_E_INVALID;
+    }
+    if (token_offset + n_tokens > 2147483647LL) {
+        set_error("token count exceeds INT_MAX");
+        return GRPO_B200_E_INVALID;
+    }
+    if (!(clip_eps >= 0.0f && clip_eps < 1.0f)) {
+        set_error("clip_eps must be finite and in [0, 1)");
+        return GRPO_B200_E_INVALID;
+    }
+    if (!(beta >= 0.0f && beta <= 3.402823466e+38f)) {
+        set_error("beta must be finite and non-negative");
+        return GRPO_B200_E_INVALID;
+    }
+
+    // Set-up, once per device and with that device current: ask the runtime where the array lives
+    // on THIS device.  Passing the symbol itself to a kernel would hand it a host-side address.
+    int dev = 0;
+    GRPO_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("device index %d is outside the range this entry point tracks", dev);
+        return GRPO_B200_E_INVALID;
+    }
+    double* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            void* ptr = nullptr;
+            GRPO_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_partials));
+            g_noalloc_ptr[dev] = static_cast<double*>(ptr);
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+
+    LossArgs a;
+    a.logp_new = logp_new;
+    a.logp_old = logp_old;
+    a.logp_ref = logp_ref;
+    a.advantages = advantages;
+    a.weights = weights;
+    a.mask = mask;
+    a.n_tokens = n_tokens;
+    a.token_offset = token_offset;
+    a.tokens_per_seq = tokens_per_seq;
+    a.clip_eps = clip_eps;
+    a.beta = beta;
+    a.dlogp = dlogp;
+    a.result = result;
+    a.partials = scratch;
+
+    // Same kernels as grpo_b200_loss, with the grid capped at the number of partial slots held here.
+    // Every block overwrites its own slot and the finalize pass reads exactly `blocks` slots, so
+    // nothing left over from an earlier call is ever read and nothing needs clearing.
+    int blocks = loss_grid_blocks(n_tokens);
+    if (blocks > kNoAllocBlocks) blocks = kNoAllocBlocks;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bool vec = aligned16(logp_new) && aligned16(logp_old) && aligned16(logp_ref) && aligned16(mask) &&
+                     aligned16(dlogp);
+    if (vec)
+        token_loss_kernel<true><<<blocks, kLossThreads, 0, s>>>(a);
+    else
+        token_loss_kernel<false><<<blocks, kLossThreads, 0, s>>>(a);
+    GRPO_CUDA_TRY(cudaGetLastError());
+    loss_finalize_kernel<<<1, 256, 0, s>>>(scratch, blocks, result);
+    GRPO_CUDA_TRY(cudaGetLastError());
+    return GRPO_B200_OK;
+}

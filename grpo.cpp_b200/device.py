@@ -100,6 +100,20 @@ def loss(logp_new, logp_old, logp_ref, advantages, weights, mask, tokens_per_seq
     return dlogp, result
 
 
+def loss_noalloc(logp_new, logp_old, logp_ref, advantages, weights, mask, tokens_per_seq: int, clip_eps: float,
+                 beta: float, *, dlogp: torch.Tensor, result: torch.Tensor, token_offset: int = 0):
+    """Selected-token path through ``grpo_b200_loss_noalloc``: the caller passes inputs and outputs
+    only (``dlogp`` and ``result`` must already exist); the library's own scratch array holds the
+    partial sums.  At most 16,777,216 tokens per call; calls that may overlap on the GPU race."""
+    _lib.check(_lib.lib().grpo_b200_loss_noalloc(
+        _check_tensor(logp_new, torch.float32, "logp_new"), _check_tensor(logp_old, torch.float32, "logp_old"),
+        _check_tensor(logp_ref, torch.float32, "logp_ref"), _check_tensor(advantages, torch.float32, "advantages"),
+        _check_tensor(weights, torch.float32, "weights"), _check_tensor(mask, torch.int32, "mask"),
+        logp_new.numel(), token_offset, tokens_per_seq, float(clip_eps), float(beta),
+        _check_tensor(dlogp, torch.float32, "dlogp"), _check_tensor(result, torch.float64, "result"), _stream()))
+    return dlogp, result
+
+
 def logits_workspace(n_rows: int, device=None) -> torch.Tensor:
     n = _lib.lib().grpo_b200_logits_workspace_bytes(n_rows)
     return torch.empty(n, dtype=torch.uint8, device=device or torch.cuda.current_device())

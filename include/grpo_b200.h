@@ -136,6 +136,29 @@ int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* lo
                    float clip_eps, float beta, float* dlogp, grpo_b200_result_t* result,
                    void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream);
 
+/* Selected-token path without any memory from the caller beyond inputs and outputs.
+ * This entry point has no counterpart in the reference.  It exists for callers that cannot call
+ * cudaMalloc and have no spare device buffer to pass as workspace: a trainer that carves all of
+ * its device memory out of one slab at start-up and has accounted for every byte of it, or code
+ * running where an allocation would stall the whole device (cudaMalloc synchronises with every
+ * stream) or is simply forbidden by the host framework's memory policy.
+ * Same arithmetic, kernels and results as grpo_b200_loss; the per-block partial sums go to a
+ * 40 KB array that the library itself holds on every GPU it is loaded on (until the process
+ * exits) instead of a caller workspace.  Limits and rules:
+ *   - at most 16,777,216 tokens per call; larger calls are refused with GRPO_B200_E_INVALID and a
+ *     message naming the limit (use grpo_b200_loss for those);
+ *   - the first call on each device looks up the array's device address (no allocation, but a
+ *     runtime query): make that first call before starting any stream capture on that device;
+ *   - all calls on one device share the array, so two calls that can overlap on the GPU (different
+ *     streams, no dependency between them) race on it and must be serialised by the caller; calls
+ *     in the same stream are safe, and nothing needs clearing between calls;
+ *   - it never calls cudaMalloc, cudaFree or any allocating library routine. */
+int grpo_b200_loss_noalloc(const float* logp_new, const float* logp_old, const float* logp_ref,
+                           const float* advantages, const float* weights, const int32_t* mask,
+                           int64_t n_tokens, int64_t token_offset, int tokens_per_seq,
+                           float clip_eps, float beta, float* dlogp, grpo_b200_result_t* result,
+                           grpo_b200_stream_t stream);
+
 /* Logits path: per active row log-softmax (max + normaliser), gather of the selected logit,
  * token loss, and the log-softmax backward dL/dlogits = dlogp * (onehot - softmax); columns
  * [V, P) and every masked row are written as zeros; masked rows and their selected id are
