@@ -32,6 +32,27 @@ def shard_rows(n_rows: int, world: int, rank: int) -> tuple[int, int]:
     return rank * base + min(rank, rem), base + (1 if rank < rem else 0)
 
 
+def shard_rows_balanced(mask, world: int, V: int, P: int) -> list[tuple[int, int]]:
+    """Contiguous row ranges ``[(row_offset, row_count), ...]`` of nearly equal HBM traffic.
+
+    An active row costs ``V + P`` floats (one read, one write), a masked row ``P`` (zeros written,
+    nothing read), so with ragged masks equal row counts are not equal work: the rank that happens
+    to hold the longest responses finishes last and everyone waits for it in the result exchange.
+    ``mask`` is the whole batch's host mask; every rank computes the same cut points from it."""
+    import numpy as np
+    m = np.asarray(mask).reshape(-1) != 0
+    cost = np.where(m, V + P, P).astype(np.int64)
+    prefix = np.concatenate(([0], np.cumsum(cost)))
+    total = int(prefix[-1])
+    cuts = [0]
+    for r in range(1, world):
+        target = total * r // world
+        cut = int(np.searchsorted(prefix, target, side="left"))
+        cuts.append(min(max(cut, cuts[-1]), m.size))
+    cuts.append(m.size)
+    return [(cuts[r], cuts[r + 1] - cuts[r]) for r in range(world)]
+
+
 class ShardedBoundary:
     """One rank's view of the sharded loss boundary.
 
@@ -43,7 +64,7 @@ class ShardedBoundary:
 
     def __init__(self, n_seq: int, tokens_per_seq: int, V: int, P: int, *, clip_eps: float = 0.2,
                  beta: float = 0.0, reduction: int = ReductionMode.token_mean, length_alpha: float = 0.0,
-                 group=None, ops=None, device=None):
+                 group=None, ops=None, device=None, rows: tuple[int, int] | None = None):
         if ops is None:
             from . import device as ops  # the CUDA library; fails loudly when it is missing
         self.ops = ops
@@ -52,7 +73,9 @@ class ShardedBoundary:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.row_offset, self.n_local = shard_rows(n_seq * tokens_per_seq, self.world, self.rank)
+        # `rows` overrides the equal-count split (e.g. one entry of shard_rows_balanced)
+        self.row_offset, self.n_local = rows if rows is not None else shard_rows(
+            n_seq * tokens_per_seq, self.world, self.rank)
         self.device = device
         self.lengths = torch.zeros(n_seq, dtype=torch.int32, device=device)
         self.weights = torch.zeros(n_seq, dtype=torch.float32, device=device)
@@ -80,6 +103,26 @@ class ShardedBoundary:
                         result=self.result, workspace=self.workspace)
         self._all_reduce(self.result)
         return self.result
+
+    def capture(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
+                kernel: int = CudaLogitsKernel.fused):
+        """Record ``prepare`` + ``step`` over these (fixed-address) tensors into a CUDA graph, so that a
+        pass is one graph launch: the eight small launches and two collectives of a pass no longer
+        wait on host dispatch, which matters once a rank's kernel time drops below a millisecond.
+        One eager pass runs first (kernel attributes, occupancy queries and NCCL set-up must not
+        happen under capture); it consumes the logits in place like any pass."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.prepare(mask_local)
+            self.step(logits_local, logp_old, logp_ref, selected, advantages, mask_local, kernel)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.prepare(mask_local)
+            self.step(logits_local, logp_old, logp_ref, selected, advantages, mask_local, kernel)
+        return graph
 
     def stats(self) -> dict:
         """Reads the records back (synchronises) and applies the reference's error contract

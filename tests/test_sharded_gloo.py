@@ -110,3 +110,19 @@ def test_shard_rows_partition():
             assert max(c for _, c in spans) - min(c for _, c in spans) <= 1
     with pytest.raises(ValueError):
         shard_rows(10, 2, 2)
+
+
+def test_balanced_shards_cover_and_balance():
+    from grpo_cpp_b200 import workloads as W
+    from grpo_cpp_b200.sharded import shard_rows_balanced
+    rng = np.random.RandomState(0)
+    T, S, V, P = 64, 96, 1000, 1024
+    mask = W.prefix_mask(rng.randint(8, T + 1, S), T)
+    cost = np.where(mask != 0, V + P, P)
+    for world in (1, 2, 3, 8):
+        spans = shard_rows_balanced(mask, world, V, P)
+        assert spans[0][0] == 0 and sum(c for _, c in spans) == mask.size
+        for (o0, c0), (o1, _) in zip(spans, spans[1:]):
+            assert o0 + c0 == o1
+        work = [int(cost[o:o + c].sum()) for o, c in spans]
+        assert max(work) - min(work) <= 2 * (V + P)  # within a row or two of each other
