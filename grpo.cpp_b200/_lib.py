@@ -31,6 +31,8 @@ SIGNATURES = {
     "grpo_b200_build_info": (C.c_char_p, []),
     "grpo_b200_count_lengths": (_int, [_vp, _i64, _i64, _int, _i64, _vp, _vp]),
     "grpo_b200_weights_from_lengths": (_int, [_vp, _i64, _int, _flt, _vp, _vp, _vp]),
+    "grpo_b200_count_lengths_f64": (_int, [_vp, _i64, _i64, _int, _i64, _vp, _vp]),
+    "grpo_b200_weights_from_lengths_f64": (_int, [_vp, _i64, _int, _flt, _vp, _vp, _vp]),
     "grpo_b200_group_advantages": (_int, [_vp, _int, _int, _int, _flt, _vp, _vp, _vp]),
     "grpo_b200_loss_workspace_bytes": (_sz, [_i64]),
     "grpo_b200_loss": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _flt, _flt, _vp, _vp, _vp, _sz, _vp]),

@@ -81,6 +81,31 @@ int grpo_b200_weights_from_lengths(const int32_t* lengths, int64_t n_seq, int re
     return GRPO_B200_OK;
 }
 
+int grpo_b200_count_lengths_f64(const int32_t* mask, int64_t n_rows, int64_t row_offset, int tokens_per_seq,
+                                int64_t n_seq, double* lengths, grpo_b200_stream_t stream) {
+    if (!mask || !lengths) return invalid("mask and lengths must not be null");
+    if (n_rows <= 0 || n_seq <= 0 || tokens_per_seq <= 0 || row_offset < 0)
+        return invalid("B, G and T must be positive");
+    if (n_seq > kIntMax) return invalid("sequence count exceeds INT_MAX");
+    if (row_offset + n_rows > n_seq * static_cast<int64_t>(tokens_per_seq))
+        return invalid("local rows reach past the end of the batch");
+    GRPO_CUDA_TRY(launch_count_lengths_f64(mask, n_rows, row_offset, tokens_per_seq, n_seq, lengths,
+                                           reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_weights_from_lengths_f64(const double* lengths, int64_t n_seq, int reduction, float length_alpha,
+                                       float* weights, int32_t* meta, grpo_b200_stream_t stream) {
+    if (!lengths || !weights || !meta) return invalid("lengths, weights and meta must not be null");
+    if (n_seq <= 0) return invalid("B, G and T must be positive");
+    if (n_seq > kIntMax) return invalid("sequence count exceeds INT_MAX");
+    if (reduction < 0 || reduction > 2) return invalid("unknown reduction mode");
+    if (!(length_alpha >= 0.0f && length_alpha <= 1.0f)) return invalid("length_alpha must be finite and in [0, 1]");
+    GRPO_CUDA_TRY(launch_weights_f64(lengths, n_seq, reduction, length_alpha, weights, meta,
+                                     reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
 int grpo_b200_group_advantages(const float* rewards, int B, int G, int mode, float eps, float* advantages,
                                int32_t* meta, grpo_b200_stream_t stream) {
     if (!rewards || !advantages || !meta) return invalid("rewards, advantages and meta must not be null");

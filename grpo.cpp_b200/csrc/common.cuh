@@ -184,6 +184,10 @@ cudaError_t launch_count_lengths(const int32_t* mask, long long n_rows, long lon
                                  cudaStream_t stream);
 cudaError_t launch_weights(const int32_t* lengths, long long n_seq, int reduction, float alpha,
                            float* weights, int32_t* meta, cudaStream_t stream);
+cudaError_t launch_count_lengths_f64(const int32_t* mask, long long n_rows, long long row_offset,
+                                     int tokens_per_seq, long long n_seq, double* lengths, cudaStream_t stream);
+cudaError_t launch_weights_f64(const double* lengths, long long n_seq, int reduction, float alpha,
+                               float* weights, int32_t* meta, cudaStream_t stream);
 cudaError_t launch_group_advantages(const float* rewards, int B, int G, int mode, float eps,
                                     float* advantages, int32_t* meta, cudaStream_t stream);
 

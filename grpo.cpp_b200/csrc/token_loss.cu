@@ -123,9 +123,11 @@ __global__ void __launch_bounds__(256) loss_finalize_kernel(const double* __rest
 }
 
 // One warp per response: counts the non-zero mask entries of its local token range.
+// LEN is int32_t, or double for the packed exchange buffer of the token-sharded path.
+template <class LEN>
 __global__ void __launch_bounds__(256) count_lengths_kernel(const int32_t* __restrict__ mask, long long n_rows,
                                                             long long row_offset, long long T, long long n_seq,
-                                                            int32_t* __restrict__ lengths) {
+                                                            LEN* __restrict__ lengths) {
     const long long seq = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 5;
     if (seq >= n_seq) return;
     const int lane = threadIdx.x & 31;
@@ -136,20 +138,21 @@ __global__ void __launch_bounds__(256) count_lengths_kernel(const int32_t* __res
     for (long long i = lo + lane; i < hi; i += 32) count += __ldg(mask + (i - row_offset)) != 0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) count += __shfl_down_sync(0xffffffffu, count, o);
-    if (lane == 0) lengths[seq] = count;
+    if (lane == 0) lengths[seq] = static_cast<LEN>(count);
 }
 
 // Single block: total of the lengths, number of empty responses, then the weights with the
 // reference's fp32 expressions (src/cuda/grpo_loss_cuda.cu:43-55).  The power is evaluated in
 // double and rounded, which reproduces a correctly rounded powf.
-__global__ void __launch_bounds__(1024) weights_kernel(const int32_t* __restrict__ lengths, long long n_seq,
+template <class LEN>
+__global__ void __launch_bounds__(1024) weights_kernel(const LEN* __restrict__ lengths, long long n_seq,
                                                        int reduction, float alpha, float* __restrict__ weights,
                                                        int32_t* __restrict__ meta) {
     __shared__ double scratch[2 * 1024 / 32];
     __shared__ double total_sh;
     double v[2] = {0.0, 0.0};
     for (long long s = threadIdx.x; s < n_seq; s += 1024) {
-        const int L = lengths[s];
+        const int L = static_cast<int>(lengths[s]);
         v[0] += static_cast<double>(L);
         v[1] += L == 0 ? 1.0 : 0.0;
     }
@@ -164,7 +167,7 @@ __global__ void __launch_bounds__(1024) weights_kernel(const int32_t* __restrict
     const float n_seq_f = static_cast<float>(n_seq);
     const float expo = __fsub_rn(alpha, 1.0f);
     for (long long s = threadIdx.x; s < n_seq; s += 1024) {
-        const int L = lengths[s];
+        const int L = static_cast<int>(lengths[s]);
         float w = 0.0f;
         if (L > 0) {
             const float Lf = static_cast<float>(L);
@@ -260,14 +263,28 @@ cudaError_t launch_count_lengths(const int32_t* mask, long long n_rows, long lon
                                  long long n_seq, int32_t* lengths, cudaStream_t stream) {
     const long long threads = n_seq * 32;
     const long long blocks = (threads + 255) / 256;
-    count_lengths_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(mask, n_rows, row_offset, tokens_per_seq,
+    count_lengths_kernel<int32_t><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(mask, n_rows, row_offset, tokens_per_seq,
                                                                             n_seq, lengths);
     return cudaGetLastError();
 }
 
 cudaError_t launch_weights(const int32_t* lengths, long long n_seq, int reduction, float alpha, float* weights,
                            int32_t* meta, cudaStream_t stream) {
-    weights_kernel<<<1, 1024, 0, stream>>>(lengths, n_seq, reduction, alpha, weights, meta);
+    weights_kernel<int32_t><<<1, 1024, 0, stream>>>(lengths, n_seq, reduction, alpha, weights, meta);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_count_lengths_f64(const int32_t* mask, long long n_rows, long long row_offset, int tokens_per_seq,
+                                     long long n_seq, double* lengths, cudaStream_t stream) {
+    const long long blocks = (n_seq * 32 + 255) / 256;
+    count_lengths_kernel<double><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(mask, n_rows, row_offset,
+                                                                                   tokens_per_seq, n_seq, lengths);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_weights_f64(const double* lengths, long long n_seq, int reduction, float alpha, float* weights,
+                               int32_t* meta, cudaStream_t stream) {
+    weights_kernel<double><<<1, 1024, 0, stream>>>(lengths, n_seq, reduction, alpha, weights, meta);
     return cudaGetLastError();
 }
 

@@ -62,6 +62,23 @@ def weights_from_lengths(lengths: torch.Tensor, reduction: int, length_alpha: fl
     return out, meta
 
 
+def count_lengths_f64(mask: torch.Tensor, n_seq: int, tokens_per_seq: int, row_offset: int, out: torch.Tensor):
+    """As :func:`count_lengths`, writing doubles into ``out[n_seq]`` (a slice of an exchange buffer)."""
+    _lib.check(_lib.lib().grpo_b200_count_lengths_f64(_check_tensor(mask, torch.int32, "mask"), mask.numel(),
+                                                     row_offset, tokens_per_seq, n_seq,
+                                                     _check_tensor(out, torch.float64, "lengths"), _stream()))
+    return out
+
+
+def weights_from_lengths_f64(lengths: torch.Tensor, reduction: int, length_alpha: float, out: torch.Tensor,
+                             meta: torch.Tensor):
+    """As :func:`weights_from_lengths`, reading the (summed) lengths as doubles."""
+    _lib.check(_lib.lib().grpo_b200_weights_from_lengths_f64(
+        _check_tensor(lengths, torch.float64, "lengths"), lengths.numel(), int(reduction), float(length_alpha),
+        _check_tensor(out, torch.float32, "weights"), _check_tensor(meta, torch.int32, "meta"), _stream()))
+    return out, meta
+
+
 def group_advantages(rewards: torch.Tensor, B: int, G: int, mode: int = 0, eps: float = 1e-8):
     """Group-relative advantages ``[B*G]``; ``meta[0]`` counts non-finite rewards/advantages."""
     r = _check_tensor(rewards, torch.float32, "rewards")

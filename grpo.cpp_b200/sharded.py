@@ -80,7 +80,10 @@ class ShardedBoundary:
         self.lengths = torch.zeros(n_seq, dtype=torch.int32, device=device)
         self.weights = torch.zeros(n_seq, dtype=torch.float32, device=device)
         self.meta = torch.zeros(2, dtype=torch.int32, device=device)
-        self.result = ops.new_result(device)
+        # one buffer for everything a pass exchanges: [0:5) the result record, [5:5+S) partial lengths
+        self.xchg = torch.zeros(5 + n_seq, dtype=torch.float64, device=device)
+        self.result = self.xchg[:5]
+        self.lengths_f64 = self.xchg[5:]
         self.workspace = ops.logits_workspace(self.n_local, device)
 
     def _all_reduce(self, t: torch.Tensor) -> None:
@@ -104,24 +107,40 @@ class ShardedBoundary:
         self._all_reduce(self.result)
         return self.result
 
+    def step_fused(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
+                   next_mask_local=None, kernel: int = CudaLogitsKernel.fused) -> torch.Tensor:
+        """One pass with ONE collective.  The weights in use come from the previous call (or from
+        ``prepare``); the partial lengths of the NEXT pass's mask (the same mask when the batch is
+        passed over again) ride in the same all-reduce as this pass's result record, and the next
+        pass's weights are derived right after it.  Masks are known long before their logits exist
+        -- rollouts precede the forward pass -- so nothing waits on anything new."""
+        nxt = mask_local if next_mask_local is None else next_mask_local
+        if nxt.numel() != self.n_local:
+            raise RuntimeError(f"mask has size {nxt.numel()}, expected {self.n_local}")
+        self.ops.count_lengths_f64(nxt, self.S, self.T, self.row_offset, self.lengths_f64)
+        self.ops.logits(logits_local, logp_old, logp_ref, selected, advantages, self.weights, mask_local,
+                        self.T, self.V, self.clip_eps, self.beta, row_offset=self.row_offset, kernel=kernel,
+                        result=self.result, workspace=self.workspace)
+        self._all_reduce(self.xchg)
+        self.ops.weights_from_lengths_f64(self.lengths_f64, self.reduction, self.alpha, self.weights, self.meta)
+        return self.result
+
     def capture(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
                 kernel: int = CudaLogitsKernel.fused):
-        """Record ``prepare`` + ``step`` over these (fixed-address) tensors into a CUDA graph, so that a
-        pass is one graph launch: the eight small launches and two collectives of a pass no longer
-        wait on host dispatch, which matters once a rank's kernel time drops below a millisecond.
+        """Record one ``step_fused`` pass over these (fixed-address) tensors into a CUDA graph, so that a
+        pass is one graph launch and its small launches do not wait on host dispatch.
         One eager pass runs first (kernel attributes, occupancy queries and NCCL set-up must not
         happen under capture); it consumes the logits in place like any pass."""
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             self.prepare(mask_local)
-            self.step(logits_local, logp_old, logp_ref, selected, advantages, mask_local, kernel)
+            self.step_fused(logits_local, logp_old, logp_ref, selected, advantages, mask_local, None, kernel)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self.prepare(mask_local)
-            self.step(logits_local, logp_old, logp_ref, selected, advantages, mask_local, kernel)
+            self.step_fused(logits_local, logp_old, logp_ref, selected, advantages, mask_local, None, kernel)
         return graph
 
     def stats(self) -> dict:

@@ -114,6 +114,17 @@ int grpo_b200_weights_from_lengths(const int32_t* lengths, int64_t n_seq, int re
                                    float length_alpha, float* weights, int32_t* meta,
                                    grpo_b200_stream_t stream);
 
+/* The same two steps with the lengths held as doubles, so that a token-sharded caller can put the
+ * partial lengths next to the five-double result record and sum both across ranks with ONE
+ * all-reduce per pass (counts are exact in a double).  Replace the same reference code as the
+ * int32 forms above (src/cuda/grpo_loss_cuda.cu:33-41 and :43-55). */
+int grpo_b200_count_lengths_f64(const int32_t* mask, int64_t n_rows, int64_t row_offset,
+                                int tokens_per_seq, int64_t n_seq, double* lengths,
+                                grpo_b200_stream_t stream);
+int grpo_b200_weights_from_lengths_f64(const double* lengths, int64_t n_seq, int reduction,
+                                       float length_alpha, float* weights, int32_t* meta,
+                                       grpo_b200_stream_t stream);
+
 /* Group-relative advantages on the device.
  * Replaces grpo::group_advantages_cpu (src/cpu/grpo_loss.cpp:16-58): per prompt, Welford mean
  * and population variance in double, all-equal groups give exact zeros.  rewards[B*G] ->

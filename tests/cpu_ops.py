@@ -46,6 +46,15 @@ def weights_from_lengths(lengths, reduction, length_alpha=0.0, out=None, meta=No
     return out, meta
 
 
+def count_lengths_f64(mask, n_seq, tokens_per_seq, row_offset, out):
+    out.copy_(count_lengths(mask, n_seq, tokens_per_seq, row_offset).to(torch.float64))
+    return out
+
+
+def weights_from_lengths_f64(lengths, reduction, length_alpha, out, meta):
+    return weights_from_lengths(lengths.to(torch.int32), reduction, length_alpha, out, meta)
+
+
 def logits(logits_t, logp_old, logp_ref, selected, advantages, weights, mask, tokens_per_seq, V, clip_eps, beta,
            *, row_offset=0, kernel=1, result=None, workspace=None, **_):
     port = oracle_py.load("port")

@@ -308,3 +308,26 @@ def test_reference_driver_against_this_library():
     out = subprocess.run([exe, "--check-only"], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "CUDA checks passed" in out.stdout and "CUDA logits checks passed" in out.stdout
+
+
+def test_fused_exchange_pass_single_rank():
+    """ShardedBoundary.step_fused at world size 1: lengths counted as doubles into the exchange
+    buffer, weights derived from it after the (no-op) collective, two passes over the same batch."""
+    import torch
+    from grpo_cpp_b200.sharded import ShardedBoundary
+    b = W.logits_case(2, 3, 8, 4099, sigma=2.0, min_len=1, reduction=W.LENGTH_WEIGHTED, length_alpha=0.5, seed=31)
+    P = 4100
+    want = run_oracle(b)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    sb = ShardedBoundary(b.S, b.T, b.V, P, clip_eps=b.clip_eps, beta=b.beta, reduction=b.reduction,
+                         length_alpha=b.length_alpha, device=torch.device("cuda"))
+    old, ref, sel, adv, mask = t(b.logp_old), t(b.logp_ref), t(b.selected), t(b.advantages), t(b.mask)
+    sb.prepare(mask)
+    for _ in range(2):
+        x = t(b.padded(P))
+        sb.step_fused(x, old, ref, sel, adv, mask)
+        got = sb.stats()
+        g3 = np.array([got["loss"], got["pg_loss"], got["kl"]])
+        assert got["valid_tokens"] == want[1]
+        assert (np.abs(g3 - want[0]) <= 1e-5 * np.abs(want[0]) + 1e-9).all()
+        assert_grad(x.cpu().numpy()[:, : b.V], want[2])

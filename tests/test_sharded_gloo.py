@@ -37,7 +37,8 @@ def _worker(rank, world, port, case, queue):
         from grpo_cpp_b200 import workloads as W
         from grpo_cpp_b200.sharded import ShardedBoundary, shard_rows
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
-        reduction, alpha, empty_mode = case
+        reduction, alpha, empty_mode = case[:3]
+        fused = len(case) > 3 and case[3]
         b = W.logits_case(2, 3, 5, 33, sigma=2.0, min_len=1, reduction=reduction, length_alpha=alpha, seed=77)
         P = 40
         if empty_mode == "globally_empty":
@@ -55,7 +56,16 @@ def _worker(rank, world, port, case, queue):
         x = torch.from_numpy(b.padded(P)[sl].copy())
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
         sb.prepare(t(b.mask[sl]))
-        sb.step(x, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages), t(b.mask[sl]))
+        if fused:
+            # two passes over the batch with one collective each: the second pass runs on the weights
+            # that rode along with the first pass's result record
+            scratch = x.clone()
+            sb.step_fused(scratch, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages),
+                          t(b.mask[sl]))
+            sb.weights_check = sb.weights.clone()
+            sb.step_fused(x, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages), t(b.mask[sl]))
+        else:
+            sb.step(x, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages), t(b.mask[sl]))
         if empty_mode == "globally_empty":
             try:
                 sb.stats()
@@ -81,7 +91,8 @@ def _worker(rank, world, port, case, queue):
             dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("case", [(1, 0.0, None), (2, 0.5, None), (0, 0.0, None),
+@pytest.mark.parametrize("case", [(1, 0.0, None), (2, 0.5, None), (0, 0.0, None), (1, 0.0, None, True),
+                                  (2, 0.5, None, True),
                                   (1, 0.0, "empty_on_rank1_only"), (1, 0.0, "globally_empty")])
 def test_two_ranks_over_gloo(case):
     world = 2
