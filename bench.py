@@ -49,6 +49,10 @@ def workload_spec(name: str) -> dict:
         s = dict(W.GPT2_SHAPE)
         s.update(reduction=W.TOKEN_MEAN, alpha=0.0, label="gpt2-124M-shaped loss boundary, token-sharded")
         return s
+    if name == "gpt2s":  # the same row shape with 1/16 of the rows: small enough for multi-pass ncu captures
+        s = dict(W.GPT2_SHAPE)
+        s.update(B=2, reduction=W.TOKEN_MEAN, alpha=0.0, label="gpt2-124M-shaped loss boundary, 4096 rows")
+        return s
     if name == "v32k":
         return dict(B=2, G=8, T=64, V=32768, P=32768, sigma=2.0, min_len=None, reduction=W.TOKEN_MEAN, alpha=0.0,
                     label="fused logits N=1024 x V=32768, full mask, token-mean")
@@ -429,7 +433,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="gpt2", choices=["gpt2", "v32k", "v128k"])
+    ap.add_argument("--workload", default="gpt2", choices=["gpt2", "gpt2s", "v32k", "v128k"])
     ap.add_argument("--variant", type=int, default=None, help="force a row-resident kernel variant")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch each pass eagerly instead of replaying a CUDA graph")
