@@ -9,11 +9,13 @@ U[32,256], token-mean reduction with the global normaliser all-reduced), the con
 headline metric -- fused loss+dlogits tokens/s and HBM GB/s at 1/2/4/8 GPUs -- is quoted on.  The
 65,536 rows are split contiguously over the ranks (total work fixed: strong scaling).
 
-A step is one pass of the hot path over the batch: mask -> per-response lengths (-> all-reduce) ->
-weights -> fused logits kernel in place -> finalize (-> all-reduce of the result record).  The
-logits are restored from a pristine copy and L2 is flushed between steps, outside the timed
-region; each step is timed with CUDA events on the launching stream and the per-rank totals are
-reduced with MAX.  One JSON line is printed by rank 0.
+A step is one pass of the hot path over the batch: fused logits kernel in place (with the weights the
+previous pass left) -> per-row loss terms -> finalize; the mask's per-response lengths are counted
+for the next pass and travel with the result record in ONE all-reduce, after which the next
+pass's weights are derived.  The logits are restored from a pristine copy and L2 is flushed between
+passes on the same stream, outside the timed event pairs; the K passes are bracketed by a barrier
+and a synchronize, each is timed by a CUDA-event pair on the launching stream, and the per-rank
+totals are reduced with MAX.  One JSON line is printed by rank 0.
 
 ``--impl reference`` times the reference's own CPU implementation of the same path
 (oracle/_ref, the reference's src/cpu/grpo_loss.cpp compiled unmodified; the C restatement when
@@ -412,7 +414,10 @@ def gpu_arm(args, spec: dict) -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_kind}",
                          "kernel": f"logits_pipelined_kernel<{plan}> (+ terms, finalize)", "ms_per_launch": k_ms,
-                         "algorithmic_bytes_per_launch": kernel_bytes, "traffic": TRAFFIC_BYTES.get(args.workload)},
+                         "algorithmic_bytes_per_launch": kernel_bytes,
+                         # the ncu-derived figure is for the whole batch on one GPU; a rank's launch moves its share
+                         "traffic": (round(TRAFFIC_BYTES[args.workload] * kernel_bytes / FULL_ALGORITHMIC[args.workload])
+                                     if args.workload in TRAFFIC_BYTES else None)},
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_single(spec)
@@ -424,7 +429,12 @@ def gpu_arm(args, spec: dict) -> None:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu
 # capture, scaled to the full launch where a smaller case was captured (see profiles/); null
 # until a capture exists for that workload.
-TRAFFIC_BYTES: dict = {}
+FULL_ALGORITHMIC = {"gpt2": 20629393828}
+TRAFFIC_BYTES: dict = {
+    # profiles/logits_pipelined_kernel_gpt2_shaped_4096_rows.txt: reads 1.0001x algorithmic (scaled by
+    # active rows), writes = algorithmic minus the ~58 MB still dirty in L2 at kernel end
+    "gpt2": 20.57e9,
+}
 
 
 def main() -> None:
