@@ -47,12 +47,12 @@ namespace grpo_b200 {
 int g_forced_variant = -1;
 
 // Build-time diagnostic (-DGRPO_TIMELINE): CTA 0 records the SM clock at the phase boundaries of
-// its first rows, for threads 0 and THREADS-1, into a device array that a debug call copies out.
+// sixteen of its active rows, for threads 0 and THREADS-1, into a device array that a debug call copies out.
 #ifdef GRPO_TIMELINE
 __device__ long long g_timeline[2][16][8];
 #define GRPO_TL(phase)                                                                          \
     do {                                                                                        \
-        if (blockIdx.x == 0 && (tid == 0 || tid == THREADS - 1) && tl_row < 16)                 \
+        if (blockIdx.x == 0 && (tid == 0 || tid == THREADS - 1) && tl_row >= 0 && tl_row < 16)  \
             g_timeline[tid == 0 ? 0 : 1][tl_row][phase] = clock64();                            \
         if ((phase) == 7) tl_row++;                                                             \
     } while (0)
@@ -244,27 +244,41 @@ __device__ __forceinline__ double term_correction(float xv, float shift) {
     return exact * (1.0 / kEx2BiasFix) - static_cast<double>(exp_rel(xv, shift));
 }
 
-// Per-CTA partial of the row reduction, exchanged through distributed shared memory.
-struct __align__(16) Exchange {
-    double s;     // normaliser of the CTA's slice relative to e^m (round 0) / heavy correction (round 1)
-    float m;      // maximum of the slice (-inf when empty)
+// One warp's partial of the row reduction.  Lane 0 of every consumer warp writes it into the same
+// slot of EVERY CTA of the cluster (its own included) and then arrives on that CTA's exchange
+// barrier, so the first thing any CTA waits for after its exponentials is the complete set.
+struct __align__(16) WarpPart {
+    double s;     // sum of the warp's terms 2^(x*log2e - shift), compensated, double corrections included
+    float m;      // maximum of the warp's columns (-inf when it holds none)
+    float shift;  // the exponent offset the warp used
     float chk;    // finiteness probe
-    float x_sel;  // the selected logit, if this CTA's slice holds it
+    float x_sel;  // the selected logit, if this warp's thread 0 found it in the CTA's slice
     int has_sel;
+    int pad;
 };
+
+// Asynchronous 32-byte store of one partial into CTA `rank`'s copy of `slot`; each 16-byte half
+// counts its bytes on that CTA's copy of `bar` when it lands (st.async, sm_90+).
+__device__ __forceinline__ void send_part(WarpPart* slot, uint64_t* bar, unsigned rank, double s, float m, float shift,
+                                          float chk, float x_sel, int has_sel) {
+    uint32_t dst, rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(smem_addr(slot)), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(smem_addr(bar)), "r"(rank));
+    const long long s_bits = __double_as_longlong(s);
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst),
+                 "r"(static_cast<int>(s_bits & 0xffffffffLL)), "r"(static_cast<int>(s_bits >> 32)), "r"(__float_as_int(m)),
+                 "r"(__float_as_int(shift)), "r"(rbar)
+                 : "memory");
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst + 16u),
+                 "r"(__float_as_int(chk)), "r"(__float_as_int(x_sel)), "r"(has_sel), "r"(0), "r"(rbar)
+                 : "memory");
+}
 
 // barrier 1: the consumer warps only (the producer warp never joins it)
 __device__ __forceinline__ void consumer_sync(int threads) {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
-// arrive (release, cluster scope) on the mbarrier that sits at the same shared-memory offset in
-// CTA `rank` of this cluster
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, unsigned rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(bar)), "r"(rank));
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -283,30 +297,6 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
         if (clock64() - start > (1LL << 32)) return false;
     }
     return true;
-}
-
-// One round of the cluster-wide exchange, run by warp 0 of every CTA of the cluster: lane p
-// pushes this CTA's record into CTA p's inbox and arrives on CTA p's mbarrier; then the warp
-// waits until all CLUSTER records have landed in its own inbox and lane r returns CTA r's.
-// Only the leader warps take part: no cluster-wide hardware barrier, nobody else waits.
-template <int CLUSTER>
-__device__ __forceinline__ Exchange cluster_exchange(Exchange mine, Exchange* inbox, uint64_t* bar, unsigned& uses,
-                                                     int lane, unsigned crank, bool& alive) {
-    cg::cluster_group cluster = cg::this_cluster();
-    if (lane < CLUSTER) {
-        *cluster.map_shared_rank(inbox + crank, lane) = mine;
-        mbar_arrive_remote(bar, lane);
-    }
-    if (alive) alive = mbar_wait_cluster(bar, uses & 1u);
-    uses++;
-    Exchange e;
-    e.s = 0.0;
-    e.m = kNegInf;
-    e.chk = 0.0f;
-    e.x_sel = 0.0f;
-    e.has_sel = 0;
-    if (lane < CLUSTER) e = inbox[lane];
-    return e;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -329,18 +319,14 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     constexpr int TILES = VEC / TJ;
     constexpr int BATCH = 256;  // rows whose scalars are staged at once
     static_assert(VEC % TJ == 0, "tiles must cover the per-thread chunks exactly");
-    static_assert(WARPS <= 32 && CLUSTER <= 32, "one lane per warp / per cluster rank in the combine step");
+    static_assert(WARPS <= 32, "warp indices fit one lane each");
 
     extern __shared__ __align__(128) unsigned char ring_raw[];
     float4* ring = reinterpret_cast<float4*>(ring_raw);
     __shared__ uint64_t full_bar[STAGES];
     __shared__ uint64_t empty_bar[STAGES];
-    __shared__ uint64_t xbar[2][2];                 // [row parity][round]: CLUSTER arrivals each
-    __shared__ Exchange inbox[2][2][CLUSTER];       // [row parity][round][source rank]
-    __shared__ float warp_m[WARPS];
-    __shared__ float warp_shift[WARPS];
-    __shared__ float warp_chk[WARPS];
-    __shared__ double warp_s[WARPS];
+    __shared__ uint64_t xbar[2];                    // [row parity]: completes when all CLUSTER * WARPS partials are in
+    __shared__ WarpPart parts[2][CLUSTER * WARPS];  // [row parity][source rank * WARPS + source warp]
     __shared__ double warp_f[WARPS];  // 2^(shift_w - M*log2e): the warp's terms relative to the row maximum
     __shared__ RowBroadcast bc;
     __shared__ int meta_sel[BATCH];
@@ -383,7 +369,8 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], WARPS);
         }
-        for (int i = 0; i < 4; i++) mbar_init(&xbar[i >> 1][i & 1], CLUSTER);
+        // one CTA: WARPS plain arrivals; a cluster: one arrival that announces the bytes, the bytes count themselves
+        for (int i = 0; i < 2; i++) mbar_init(&xbar[i], CLUSTER == 1 ? WARPS : 1);
         q_cons_final = 0;
         abort_sh = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -398,9 +385,12 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     unsigned q = 0;     // consumers: tiles consumed; producer: tiles requested
     bool alive = true;  // false after a wait timed out: skip the ring, keep meeting barriers
     unsigned row_parity = 0;
-    unsigned xuses[2][2] = {{0u, 0u}, {0u, 0u}};
+    unsigned xuses[2] = {0u, 0u};
 #ifdef GRPO_TIMELINE
-    int tl_row = 0;
+#ifndef GRPO_TL_SKIP
+#define GRPO_TL_SKIP 0
+#endif
+    int tl_row = -(GRPO_TL_SKIP);  // active rows of CTA 0 to let pass before recording starts
 #endif
 
     for (int batch_first = 0; batch_first < n_mine; batch_first += BATCH) {
@@ -542,16 +532,20 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             float m = kNegInf, m2 = kNegInf;
 #pragma unroll
             for (int j = 0; j < VEC; j++) {
-                if (CHECK) {
-                    // x * 0 is NaN for an infinite or NaN logit and 0 otherwise; -inf marks "no column here"
-                    if (x[j].x != kNegInf) chk = fmaf(x[j].x, 0.0f, chk);
-                    if (x[j].y != kNegInf) chk = fmaf(x[j].y, 0.0f, chk);
-                    if (x[j].z != kNegInf) chk = fmaf(x[j].z, 0.0f, chk);
-                    if (x[j].w != kNegInf) chk = fmaf(x[j].w, 0.0f, chk);
+                // uniform test, made only inside the last tile so that the chunks before it schedule as one block:
+                // does chunk index j hold columns for any thread of this CTA?
+                if (j < VEC - TJ || j * THREADS < n_load) {
+                    if (CHECK) {
+                        // x * 0 is NaN for an infinite or NaN logit and 0 otherwise; -inf marks "no column here"
+                        if (x[j].x != kNegInf) chk = fmaf(x[j].x, 0.0f, chk);
+                        if (x[j].y != kNegInf) chk = fmaf(x[j].y, 0.0f, chk);
+                        if (x[j].z != kNegInf) chk = fmaf(x[j].z, 0.0f, chk);
+                        if (x[j].w != kNegInf) chk = fmaf(x[j].w, 0.0f, chk);
+                    }
+                    const float cm = max4(x[j]);
+                    m2 = fmaxf(m2, fminf(m, cm));
+                    m = fmaxf(m, cm);
                 }
-                const float cm = max4(x[j]);
-                m2 = fmaxf(m2, fminf(m, cm));
-                m = fmaxf(m, cm);
             }
 
             // ---- one exp per element relative to the warp's maximum; compensated fp32 sums (four
@@ -563,11 +557,13 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             float2 sa = make_float2(0.0f, 0.0f), nca = sa, sb = sa, ncb = sa;
 #pragma unroll
             for (int j = 0; j < VEC; j++) {
-                const float2 ea = exp_rel2(lo2(x[j]), neg_shift2);
-                const float2 eb = exp_rel2(hi2(x[j]), neg_shift2);
-                x[j] = make_float4(ea.x, ea.y, eb.x, eb.y);
-                kahan_add2(sa, nca, ea);
-                kahan_add2(sb, ncb, eb);
+                if (j < VEC - TJ || j * THREADS < n_load) {
+                    const float2 ea = exp_rel2(lo2(x[j]), neg_shift2);
+                    const float2 eb = exp_rel2(hi2(x[j]), neg_shift2);
+                    x[j] = make_float4(ea.x, ea.y, eb.x, eb.y);
+                    kahan_add2(sa, nca, ea);
+                    kahan_add2(sb, ncb, eb);
+                }
             }
             const double s_thread = ((static_cast<double>(sa.x) + static_cast<double>(nca.x)) +
                                      (static_cast<double>(sa.y) + static_cast<double>(nca.y))) +
@@ -580,48 +576,73 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             GRPO_TL(2);  // exp + compensated sums done
             const double s_warp = warp_sum_all(s_fixed);
             if (CHECK) chk = warp_sum_f(chk);
-            if (lane == 0) {
-                warp_m[warp] = m_warp;
-                warp_shift[warp] = shift;
-                warp_s[warp] = s_warp;
-                if (CHECK) warp_chk[warp] = chk;
-            }
-            consumer_sync(THREADS);
-            GRPO_TL(3);  // past the first block barrier
 
-            // ---- CTA combine, then cluster exchange (warp 0): factors in double, fixed shuffle trees
+            // ---- every warp hands its partial to every CTA of the cluster: lane p sends it to CTA p
+            //      with asynchronous stores that count their bytes on CTA p's exchange barrier, so the
+            //      sender waits for nothing
+            if (CLUSTER == 1) {
+                if (lane == 0) {
+                    WarpPart mine;
+                    mine.s = s_warp;
+                    mine.m = m_warp;
+                    mine.shift = shift;
+                    mine.chk = chk;
+                    mine.x_sel = x_sel;  // zero except in thread 0
+                    mine.has_sel = has_sel;
+                    mine.pad = 0;
+                    parts[row_parity][warp] = mine;
+                    mbar_arrive(&xbar[row_parity]);
+                }
+            } else {
+                const float xs0 = __shfl_sync(0xffffffffu, x_sel, 0);  // zero except in warp 0
+                const int hs0 = __shfl_sync(0xffffffffu, has_sel, 0);
+                if (tid == 0) mbar_arrive_expect_tx(&xbar[row_parity], CLUSTER * WARPS * sizeof(WarpPart));
+                if (lane < CLUSTER)
+                    send_part(&parts[row_parity][crank * WARPS + warp], &xbar[row_parity], static_cast<unsigned>(lane),
+                              s_warp, m_warp, shift, chk, xs0, hs0);
+            }
+            GRPO_TL(3);  // partial handed over
+
+            // ---- warp 0 of every CTA combines all partials of the row: same slots, same order,
+            //      same bits in every CTA.  Factors in double, fixed shuffle trees.
             if (warp == 0) {
-                const float ml = lane < WARPS ? warp_m[lane] : kNegInf;
-                const float m_cta = warp_max(ml);
-                double f = 0.0, s = 0.0;  // lane w: scale of warp w's terms relative to e^m_cta
-                float c = 0.0f;
-                if (lane < WARPS && ml != kNegInf) {
-                    // the warp's terms are 2^(x*log2e - shift_w); relative to e^m_cta they scale by this
-                    f = exp2(static_cast<double>(warp_shift[lane]) - static_cast<double>(m_cta) * kLog2eD) * kEx2BiasFix;
-                    s = warp_s[lane] * f;
+                constexpr int PARTS = CLUSTER * WARPS;
+                constexpr int PER_LANE = (PARTS + 31) / 32;
+                if (alive)
+                    alive = CLUSTER > 1 ? mbar_wait_cluster(&xbar[row_parity], xuses[row_parity] & 1u)
+                                        : mbar_wait(&xbar[row_parity], xuses[row_parity] & 1u);
+                xuses[row_parity]++;
+                GRPO_TL(4);  // all partials have landed (thread 0 only)
+                const WarpPart* in = parts[row_parity];
+                float m_lane = kNegInf;
+#pragma unroll
+                for (int i = 0; i < PER_LANE; i++) {
+                    const int idx = lane + 32 * i;
+                    if (idx < PARTS) m_lane = fmaxf(m_lane, in[idx].m);
                 }
-                if (CHECK && lane < WARPS) c = warp_chk[lane];
-                s = warp_sum_all(s);
+                const float m_row = warp_max(m_lane);
+                const double row_shift = static_cast<double>(m_row) * kLog2eD;
+                double s = 0.0;
+                float c = 0.0f, xs = 0.0f;
+#pragma unroll
+                for (int i = 0; i < PER_LANE; i++) {
+                    const int idx = lane + 32 * i;
+                    if (idx < PARTS) {
+                        const WarpPart part = in[idx];
+                        // the warp's terms are 2^(x*log2e - shift); relative to e^m_row they scale by f
+                        double f = 0.0;
+                        if (part.m != kNegInf)
+                            f = exp2_small_d(fmax(static_cast<double>(part.shift) - row_shift, -1000.0)) * kEx2BiasFix;
+                        s += part.s * f;
+                        if (CHECK) c += part.chk;
+                        if (part.has_sel) xs += part.x_sel;  // exactly one warp of the cluster holds it
+                        if (idx / WARPS == static_cast<int>(crank)) warp_f[idx % WARPS] = f;
+                    }
+                }
+                const double z_row = warp_sum_all(s);
                 if (CHECK) c = warp_sum_f(c);
-                float m_row = m_cta;
-                double z_row = s;
-                if (CLUSTER > 1) {
-                    Exchange mine;
-                    mine.s = s;
-                    mine.m = m_cta;
-                    mine.chk = c;
-                    mine.x_sel = __shfl_sync(0xffffffffu, x_sel, 0);
-                    mine.has_sel = __shfl_sync(0xffffffffu, has_sel, 0);
-                    const Exchange e = cluster_exchange<CLUSTER>(mine, inbox[row_parity][0], &xbar[row_parity][0],
-                                                                 xuses[row_parity][0], lane, crank, alive);
-                    m_row = warp_max(e.m);
-                    const double fr = e.m == kNegInf ? 0.0 : exp(static_cast<double>(e.m) - static_cast<double>(m_row));
-                    z_row = warp_sum_all(e.s * fr);
-                    if (CHECK) c = warp_sum_f(e.chk);
-                    x_sel = warp_sum_f(e.has_sel ? e.x_sel : 0.0f);  // exactly one CTA holds the selected column
-                    f *= m_cta == kNegInf ? 0.0 : exp(static_cast<double>(m_cta) - static_cast<double>(m_row));
-                }
-                if (lane < WARPS) warp_f[lane] = f;
+                x_sel = warp_sum_f(xs);
+                GRPO_TL(5);  // row maximum and normaliser known (thread 0 only)
                 // ---- row leader: dlogp for the backward sweep and the row's record.  Every CTA of
                 //      the cluster repeats it on the same bits; rank 0 writes the record.
                 if (lane == 0)
@@ -630,10 +651,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                                          bad_sel || (CHECK && c != 0.0f) || !alive, crank == 0);
             }
             consumer_sync(THREADS);
-            GRPO_TL(4);  // combine + leader done
-
-            GRPO_TL(5);  // (no separate correction phase)
-            GRPO_TL(6);  // leader done
+            GRPO_TL(6);  // leader done, everyone past the second block barrier
             // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
             const RowBroadcast b = bc;
             const float coef = static_cast<float>(warp_f[warp]) * b.neg_g_over_z;
