@@ -50,6 +50,7 @@ int g_forced_variant = -1;
 // sixteen of its active rows, for threads 0 and THREADS-1, into a device array that a debug call copies out.
 #ifdef GRPO_TIMELINE
 __device__ long long g_timeline[2][16][8];
+__device__ int g_timeline_grid;
 #define GRPO_TL(phase)                                                                          \
     do {                                                                                        \
         if (blockIdx.x == 0 && (tid == 0 || tid == THREADS - 1) && tl_row >= 0 && tl_row < 16)  \
@@ -391,6 +392,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
 #define GRPO_TL_SKIP 0
 #endif
     int tl_row = -(GRPO_TL_SKIP);  // active rows of CTA 0 to let pass before recording starts
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_timeline_grid = static_cast<int>(gridDim.x);
 #endif
 
     for (int batch_first = 0; batch_first < n_mine; batch_first += BATCH) {
@@ -982,6 +984,10 @@ bool variant_fits(int variant, int P) {
 extern "C" int grpo_b200_debug_timeline(long long* host_out) {
     return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(g_timeline)) == cudaSuccess ? 0 : 3;
 }
+extern "C" int grpo_b200_debug_grid() {
+    int g = -1;
+    return cudaMemcpyFromSymbol(&g, g_timeline_grid, sizeof(g)) == cudaSuccess ? g : -1;
+}
 #endif
 
 int resident_variant_count() { return kNumVariants; }
@@ -997,7 +1003,8 @@ int pick_resident_variant(const void* logits, const void* dlogits, int V, int P)
     if ((reinterpret_cast<uintptr_t>(logits) & 15u) || (reinterpret_cast<uintptr_t>(dlogits) & 15u)) return -1;
     if (g_forced_variant >= 0 && g_forced_variant < kNumVariants)
         return variant_fits(g_forced_variant, P) ? g_forced_variant : -1;
-    static const int order[] = {14, 4, 0, 1, 2, 3};  // smallest configuration that holds the row
+    // smallest CTAs whose cluster (at most 8) holds the row: four CTAs per SM overlap one another's serial phases
+    static const int order[] = {14, 15, 16, 17, 7, 3};
     for (int idx : order)
         if (variant_fits(idx, P)) return idx;
     return -1;
