@@ -305,7 +305,7 @@ def gpu_arm(args, spec: dict) -> None:
         e1.record()
 
     # ---- device-resident steps -------------------------------------------------------------
-    # The pass (8 small launches + 2 collectives around the big kernel) is captured once into a
+    # The pass (lengths, row kernel, reduce kernel, weights) is captured once into a
     # CUDA graph and replayed; an eager loop afterwards times the dominant kernel on its own.
     sampler = ClockSampler(local_rank) if rank == 0 else None
     graph = None
@@ -317,13 +317,17 @@ def gpu_arm(args, spec: dict) -> None:
         graph = sb.capture(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
 
     sb.prepare(devt["mask"])  # weights for the first pass; every later pass gets them from the pass before
+    peer = world > 1 and args.exchange == "peer"
+    if peer:
+        sb.enable_peer_exchange()
+    one_pass = sb.step_peer if peer else sb.step_fused
 
     def timed_pass(e0, e1):
         e0.record()
         if graph is not None:
             graph.replay()
         else:
-            sb.step_fused(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
+            one_pass(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
         e1.record()
 
     # Restore + flush run on the same stream between the timed passes and the host never waits inside
@@ -342,7 +346,7 @@ def gpu_arm(args, spec: dict) -> None:
     t_wall = time.perf_counter() - t_wall0
     step_ms = [e0.elapsed_time(e1) for e0, e1 in pairs]
     kern_ms = []
-    for i in range(3 + min(args.steps, 10)):  # dominant kernel alone (with its terms/finalize tail)
+    for i in range(3 + min(args.steps, 10)):  # dominant kernel alone (with the reduce kernel behind it)
         restore()
         barrier()
         e0, e1, k0, k1 = ev(), ev(), ev(), ev()
@@ -373,7 +377,10 @@ def gpu_arm(args, spec: dict) -> None:
             for k in host:
                 devt[k].copy_(host[k], non_blocking=True)
             sb.prepare(devt["mask"])
-            sb.step(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
+            if peer:
+                sb.step_peer(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
+            else:
+                sb.step(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
             loss_val = sb.stats()["loss"]
         dt = time.perf_counter() - t0
         if i >= args.warmup:
@@ -399,6 +406,8 @@ def gpu_arm(args, spec: dict) -> None:
                        "parallelism": f"token-sharded x{world}", "in_place": True, "kernel": plan,
                        "launch": "eager" if graph is None else "one CUDA graph per pass",
                        "sharding": "contiguous row ranges of equal traffic" if world > 1 else "single range",
+                       "exchange": ("none" if world == 1 else "reduce kernel over NVLink peer memory" if peer else
+                                    "one NCCL all-reduce per pass"),
                        "l2": "logits restored from a pristine copy and a 256 MB buffer written between passes on "
                              "the same stream, outside the timed event pairs; per-rank logits far exceed the "
                              "126 MB L2"},
@@ -410,10 +419,11 @@ def gpu_arm(args, spec: dict) -> None:
                     "d2h_bytes_per_step": 48, "ms_per_step": 1e3 * e2e_total / args.steps,
                     "api": "grpo_logits_cuda_device_inplace (host metadata, device logits)" if world == 1 else
                            "ShardedBoundary.prepare+step+stats from pinned host metadata"},
-            "gpu_launches": 5 * args.steps * world,
+            # per pass and rank: next pass's lengths, the row kernel, the reduce kernel, next pass's weights
+            "gpu_launches": 4 * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                         "kernel": f"logits_pipelined_kernel<{plan}> (+ terms, finalize)", "ms_per_launch": k_ms,
+                         "kernel": f"logits_pipelined_kernel<{plan}> (+ reduce kernel)", "ms_per_launch": k_ms,
                          "algorithmic_bytes_per_launch": kernel_bytes,
                          # the ncu-derived figure is for the whole batch on one GPU; a rank's launch moves its share
                          "traffic": (round(TRAFFIC_BYTES[args.workload] * kernel_bytes / FULL_ALGORITHMIC[args.workload])
@@ -423,6 +433,9 @@ def gpu_arm(args, spec: dict) -> None:
             line["cpu_baseline"] = cpu_baseline_single(spec)
         print(json.dumps(line), flush=True)
     if world > 1:
+        if peer:
+            barrier()  # no rank unmaps a region that another rank's kernel may still write to
+            sb.exchange.close()
         dist.destroy_process_group()
 
 
@@ -446,6 +459,9 @@ def main() -> None:
     ap.add_argument("--workload", default="gpt2", choices=["gpt2", "gpt2s", "v32k", "v128k"])
     ap.add_argument("--variant", type=int, default=None, help="force a row-resident kernel variant")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="at more than one rank: the pass's exchange by the library's own kernel over NVLink peer "
+                         "memory, or by one NCCL all-reduce")
     ap.add_argument("--no-graph", action="store_true", help="launch each pass eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     import grpo_cpp_b200  # noqa: F401  (registers the package under its importable name)

@@ -2,6 +2,7 @@
 // synchronises or exits; every pointer is a device pointer on the current device.
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
 #include <string>
 
 #include "common.cuh"
@@ -157,15 +158,23 @@ int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* lo
 }
 
 size_t grpo_b200_logits_workspace_bytes(int64_t n_rows) {
-    // one 32-byte record per row, then one 32-byte slot for the kernel's status word
-    return n_rows > 0 ? static_cast<size_t>(n_rows) * sizeof(RowRecord) + 32 : 0;
+    // one 32-byte record per row, one 32-byte slot for the status word and the ticket counter,
+    // then five doubles per block of 256 rows for the reduce kernel
+    if (n_rows <= 0) return 0;
+    const size_t blocks = (static_cast<size_t>(n_rows) + 255) / 256;
+    return static_cast<size_t>(n_rows) * sizeof(RowRecord) + 32 + blocks * 5 * sizeof(double);
 }
 
-int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
-                     const int32_t* selected, const float* advantages, const float* weights, const int32_t* mask,
-                     int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P, float clip_eps,
-                     float beta, int kernel, int check_inputs, float* selected_logp, grpo_b200_result_t* result,
-                     void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream) {
+}  // extern "C"
+
+namespace {
+
+// The whole device-side pass: row kernel, then the reduce kernel (with or without the exchange).
+int logits_pass(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
+                const int32_t* selected, const float* advantages, const float* weights, const int32_t* mask,
+                int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P, float clip_eps, float beta,
+                int kernel, int check_inputs, float* selected_logp, grpo_b200_result_t* result, void* workspace,
+                size_t workspace_bytes, const ExchangeArgs& x, grpo_b200_stream_t stream) {
     if (!logits || !dlogits) return invalid("logits_and_dlogits must not be null");
     if (!logp_old || !logp_ref || !selected || !advantages || !weights || !mask || !result)
         return invalid("device pointers must not be null");
@@ -201,16 +210,106 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
     a.selected_logp = selected_logp;
     a.result = result;
     a.status = reinterpret_cast<int*>(a.rows + n_rows);
+    a.counter = reinterpret_cast<unsigned*>(a.status) + 1;
+    a.partials = reinterpret_cast<double*>(reinterpret_cast<unsigned char*>(a.status) + 32);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    GRPO_CUDA_TRY(cudaMemsetAsync(a.status, 0, 16, s));
+    GRPO_CUDA_TRY(cudaMemsetAsync(a.status, 0, 32, s));
     const int variant = kernel == GRPO_B200_LOGITS_FUSED ? pick_resident_variant(logits, dlogits, V, P) : -1;
     if (variant >= 0)
         GRPO_CUDA_TRY(launch_logits_resident(variant, check_inputs != 0, a, s));
     else
         GRPO_CUDA_TRY(launch_logits_streaming(check_inputs != 0, a, s));
-    GRPO_CUDA_TRY(launch_logits_terms(a, s));
-    GRPO_CUDA_TRY(launch_logits_finalize(a, s));
+    GRPO_CUDA_TRY(launch_logits_reduce(a, x, s));
     return GRPO_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
+                     const int32_t* selected, const float* advantages, const float* weights, const int32_t* mask,
+                     int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P, float clip_eps,
+                     float beta, int kernel, int check_inputs, float* selected_logp, grpo_b200_result_t* result,
+                     void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream) {
+    ExchangeArgs x = {};
+    return logits_pass(logits, dlogits, logp_old, logp_ref, selected, advantages, weights, mask, n_rows, row_offset,
+                       tokens_per_seq, V, P, clip_eps, beta, kernel, check_inputs, selected_logp, result, workspace,
+                       workspace_bytes, x, stream);
+}
+
+size_t grpo_b200_exchange_bytes(int64_t n_seq) {
+    if (n_seq <= 0) return 0;
+    return kExchangeHeaderBytes + static_cast<size_t>(2 * kExchangeMaxWorld) * exchange_stride(n_seq) * sizeof(double);
+}
+
+int grpo_b200_exchange_create(int64_t n_seq, void** region) {
+    if (!region || n_seq <= 0) return invalid("region must not be null and n_seq must be positive");
+    void* p = nullptr;
+    GRPO_CUDA_TRY(cudaMalloc(&p, grpo_b200_exchange_bytes(n_seq)));
+    cudaError_t err = cudaMemset(p, 0, grpo_b200_exchange_bytes(n_seq));
+    if (err == cudaSuccess) err = cudaDeviceSynchronize();
+    if (err != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(err, "clearing the exchange region");
+    }
+    *region = p;
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_exchange_export(void* region, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is passed around as 64 bytes");
+    if (!region || !handle) return invalid("region and handle must not be null");
+    cudaIpcMemHandle_t h;
+    GRPO_CUDA_TRY(cudaIpcGetMemHandle(&h, region));
+    memcpy(handle, &h, sizeof(h));
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_exchange_open(const unsigned char handle[64], void** peer_region) {
+    if (!handle || !peer_region) return invalid("handle and peer_region must not be null");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    GRPO_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *peer_region = p;
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_exchange_close(void* peer_region) {
+    if (!peer_region) return GRPO_B200_OK;
+    GRPO_CUDA_TRY(cudaIpcCloseMemHandle(peer_region));
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_exchange_destroy(void* region) {
+    if (!region) return GRPO_B200_OK;
+    GRPO_CUDA_TRY(cudaFree(region));
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
+                             const int32_t* selected, const float* advantages, const float* weights,
+                             const int32_t* mask, int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P,
+                             float clip_eps, float beta, int kernel, int check_inputs, float* selected_logp,
+                             grpo_b200_result_t* result, void* workspace, size_t workspace_bytes,
+                             void* const* regions, int rank, int world, double* lengths, int64_t n_seq,
+                             grpo_b200_stream_t stream) {
+    if (world < 1 || world > kExchangeMaxWorld) return invalid("world must lie in [1, 8]");
+    if (rank < 0 || rank >= world) return invalid("rank must lie in [0, world)");
+    if (!regions || !lengths || n_seq <= 0) return invalid("regions and lengths must not be null and n_seq must be positive");
+    ExchangeArgs x = {};
+    for (int r = 0; r < world; r++) {
+        if (!regions[r]) return invalid("every rank's exchange region must be mapped");
+        x.peers[r] = static_cast<unsigned char*>(regions[r]);
+    }
+    x.rank = rank;
+    x.world = world;
+    x.n_seq = n_seq;
+    x.lengths = lengths;
+    return logits_pass(logits, dlogits, logp_old, logp_ref, selected, advantages, weights, mask, n_rows, row_offset,
+                       tokens_per_seq, V, P, clip_eps, beta, kernel, check_inputs, selected_logp, result, workspace,
+                       workspace_bytes, x, stream);
 }
 
 int grpo_b200_logits_set_variant(int variant) {

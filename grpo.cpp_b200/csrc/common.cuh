@@ -136,9 +136,9 @@ struct LossArgs {
 int loss_grid_blocks(long long n_tokens);
 cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream);
 
-// What the row kernels leave per active row for the terms kernel: the normaliser (relative to
+// What the row kernels leave per active row for the reduce kernel: the normaliser (relative to
 // e^m, double), the row maximum, the gathered selected logit and the input-error flags.  The
-// terms kernel overwrites the first 16 bytes with {w*loss, w*pg, w*kl, flags} for the final sum.
+// reduce kernel turns it into the row's loss terms.
 struct __align__(32) RowRecord {
     double z;
     float m;
@@ -161,10 +161,28 @@ struct LogitsArgs {
     int tokens_per_seq;
     int V, P;
     float clip_eps, beta;
-    RowRecord* rows;    // [n_rows] per-row hand-over between the row kernel and the terms kernel
+    RowRecord* rows;    // [n_rows] per-row hand-over between the row kernel and the reduce kernel
     float* selected_logp;
     grpo_b200_result_t* result;
-    int* status;  // set non-zero when a bounded pipeline wait gave up
+    int* status;        // set non-zero when a bounded pipeline wait gave up
+    unsigned* counter;  // ticket counter of the reduce kernel's blocks (zeroed with the status word)
+    double* partials;   // [ceil(n_rows / 256)][5] per-block sums of the reduce kernel
+};
+
+// The exchange region of one rank (device memory that every rank of the box maps): a header of
+// sequence numbers flags[2][8] and the region's own pass counter, then slots[2][8][stride] doubles;
+// [buffer = pass & 1][source rank].
+constexpr int kExchangeMaxWorld = 8;
+constexpr int kExchangePassOffset = 128;
+constexpr int kExchangeHeaderBytes = 256;
+__host__ __device__ inline long long exchange_stride(long long n_seq) { return (5 + n_seq + 1) & ~1LL; }
+
+struct ExchangeArgs {
+    unsigned char* peers[kExchangeMaxWorld];  // every rank's region as mapped into this process; [rank] is this GPU's own
+    int rank;
+    int world;  // 0: no exchange, the record goes straight to `result`
+    long long n_seq;
+    double* lengths;  // [n_seq] in: this rank's partial response lengths; out: their sums over ranks
 };
 // flags stored in row_terms.w (small integers, exact in fp32)
 constexpr float kRowBadGrad = 1.0f;
@@ -176,8 +194,7 @@ int resident_variant_count();
 extern int g_forced_variant;
 cudaError_t launch_logits_resident(int variant, bool check, const LogitsArgs& a, cudaStream_t stream);
 cudaError_t launch_logits_streaming(bool check, const LogitsArgs& a, cudaStream_t stream);
-cudaError_t launch_logits_terms(const LogitsArgs& a, cudaStream_t stream);
-cudaError_t launch_logits_finalize(const LogitsArgs& a, cudaStream_t stream);
+cudaError_t launch_logits_reduce(const LogitsArgs& a, const ExchangeArgs& x, cudaStream_t stream);
 
 cudaError_t launch_count_lengths(const int32_t* mask, long long n_rows, long long row_offset,
                                  int tokens_per_seq, long long n_seq, int32_t* lengths,

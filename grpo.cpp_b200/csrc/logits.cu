@@ -35,7 +35,7 @@
 //
 // Neither kernel touches a masked row's logits or selected id; both write zeros over all P
 // columns of a masked row and over columns [V, P) of an active one.  Per-row loss terms go to a
-// workspace and are summed in a fixed order by a finalize kernel.
+// workspace and are summed in a fixed order by the reduce kernel.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -147,7 +147,7 @@ __device__ __forceinline__ RowScalars load_row_scalars(const LogitsArgs& a, long
 
 // The row's serial section, kept short: dlogp for the backward sweep from fp32 device math
 // (log, exp, expm1: a few ulp, far inside the gradient's tolerance), and the row record for the
-// terms kernel, which redoes the same step in double, off this kernel's critical path, for the
+// reduce kernel, which redoes the same step in double, off this kernel's critical path, for the
 // three loss sums (a cancelling sum that needs the reference's double log-sum-exp).
 // z is the normaliser relative to e^row_max.  Follows src/cpu/grpo_loss.cpp:214-215, :137-160.
 __device__ __forceinline__ RowBroadcast row_leader_fast(const LogitsArgs& a, long long row, float row_max, double z,
@@ -820,51 +820,136 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
     for (int v = V + tid; v < P; v += kStreamThreads) out[v] = 0.0f;
 }
 
-// Terms kernel: one thread per row redoes the row's scalar step in double -- log-sum-exp,
-// log p(selected) rounded to fp32 exactly as the reference rounds it, the two exponentials --
-// and leaves {w*loss, w*pg, w*kl, flags} in the first 16 bytes of the row's record.
-__global__ void __launch_bounds__(128) logits_terms_kernel(const LogitsArgs a) {
-    const long long row = static_cast<long long>(blockIdx.x) * 128 + threadIdx.x;
-    if (row >= a.n_rows) return;
-    float4 out = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    float lp_new = 0.0f;
-    if (a.mask[row] != 0) {
-        const RowRecord r = a.rows[row];
-        const RowScalars sc = load_row_scalars(a, row);
-        const double lse = static_cast<double>(r.m) + log(r.z);
-        lp_new = static_cast<float>(static_cast<double>(r.x_sel) - lse);
-        const TokenTerms t = token_terms<true>(lp_new, sc.lp_old, sc.lp_ref, sc.adv, sc.w, a.clip_eps, a.beta);
-        float flags = r.flags;
-        if (!finite_f(t.grad) || !finite_f(t.grad / static_cast<float>(r.z))) flags += kRowBadGrad;
-        out = make_float4(t.loss, t.pg, t.kl, flags);
-    }
-    *reinterpret_cast<float4*>(a.rows + row) = out;
-    if (a.selected_logp) a.selected_logp[row] = lp_new;
+// Reduce kernel, the second and last launch of a pass.
+//
+// 1. One thread per row redoes the row's scalar step in double -- log-sum-exp, log p(selected)
+//    rounded to fp32 exactly as the reference rounds it, the two exponentials -- and each block of
+//    256 rows leaves its five sums (fixed tree) in its own slot of the workspace.
+// 2. The block that finishes last (a ticket counter; no floating-point atomics anywhere) adds the
+//    slots in index order, so the totals depend on the row count only, never on scheduling.
+// 3. Sharded runs: the same block then carries out the pass's only exchange itself.  It writes
+//    the record, followed by this rank's partial response lengths for the next pass, into its
+//    slot of every rank's exchange region over NVLink, publishes a per-slot sequence number with
+//    a system-scope release, waits (bounded) for the other ranks' numbers, and adds the slots in
+//    rank order -- the same bits on every rank.  A non-zero status word (a pipeline wait timed
+//    out) turns bad_inputs into -1, an exchange that timed out into -2.
+constexpr int kReduceThreads = 256;
+
+__device__ __forceinline__ unsigned long long* exchange_flag(unsigned char* region, int buf, int src) {
+    return reinterpret_cast<unsigned long long*>(region) + buf * kExchangeMaxWorld + src;
+}
+__device__ __forceinline__ double* exchange_slot(unsigned char* region, long long stride, int buf, int src) {
+    return reinterpret_cast<double*>(region + kExchangeHeaderBytes) + (buf * kExchangeMaxWorld + src) * stride;
 }
 
-// One block sums the per-row terms in a fixed order (double accumulators).  A non-zero status
-// word (a pipeline wait timed out) turns the record's bad_inputs negative.
-__global__ void __launch_bounds__(1024) logits_finalize_kernel(const RowRecord* __restrict__ rows, long long n_rows,
-                                                               const int* __restrict__ status,
-                                                               grpo_b200_result_t* result) {
-    __shared__ double scratch[5 * 1024 / 32];
+__global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const LogitsArgs a, const ExchangeArgs x) {
+    __shared__ double scratch[5 * kReduceThreads / 32];
+    __shared__ double record[5];
+    __shared__ int is_last, timed_out;
+    __shared__ unsigned long long pass_sh;
+    const int tid = threadIdx.x;
+    const long long row = static_cast<long long>(blockIdx.x) * kReduceThreads + tid;
     double v[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
-    for (long long r = threadIdx.x; r < n_rows; r += 1024) {
-        const float4 t = *reinterpret_cast<const float4*>(rows + r);
-        v[0] += static_cast<double>(t.x);
-        v[1] += static_cast<double>(t.y);
-        v[2] += static_cast<double>(t.z);
-        const int flags = static_cast<int>(t.w);
-        v[3] += (flags & 1) ? 1.0 : 0.0;
-        v[4] += (flags & 2) ? 1.0 : 0.0;
+    if (row < a.n_rows) {
+        float lp_new = 0.0f;
+        if (a.mask[row] != 0) {
+            const RowRecord r = a.rows[row];
+            const RowScalars sc = load_row_scalars(a, row);
+            const double lse = static_cast<double>(r.m) + log(r.z);
+            lp_new = static_cast<float>(static_cast<double>(r.x_sel) - lse);
+            const TokenTerms t = token_terms<true>(lp_new, sc.lp_old, sc.lp_ref, sc.adv, sc.w, a.clip_eps, a.beta);
+            v[0] = static_cast<double>(t.loss);
+            v[1] = static_cast<double>(t.pg);
+            v[2] = static_cast<double>(t.kl);
+            if (!finite_f(t.grad) || !finite_f(t.grad / static_cast<float>(r.z))) v[3] = 1.0;
+            if (r.flags != 0.0f) v[4] = 1.0;
+        }
+        if (a.selected_logp) a.selected_logp[row] = lp_new;
     }
-    block_sum<1024, 5>(v, scratch);
-    if (threadIdx.x == 0) {
-        result->loss = v[0];
-        result->pg_loss = v[1];
-        result->kl = v[2];
-        result->bad_grads = v[3];
-        result->bad_inputs = *status != 0 ? -1.0 : v[4];
+    block_sum<kReduceThreads, 5>(v, scratch);
+    if (tid == 0) {
+#pragma unroll
+        for (int k = 0; k < 5; k++) a.partials[static_cast<size_t>(blockIdx.x) * 5 + k] = v[k];
+        __threadfence();
+        is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+        timed_out = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    double t[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
+    for (unsigned b = tid; b < gridDim.x; b += kReduceThreads) {
+#pragma unroll
+        for (int k = 0; k < 5; k++) t[k] += __ldcg(a.partials + static_cast<size_t>(b) * 5 + k);
+    }
+    block_sum<kReduceThreads, 5>(t, scratch);
+    if (tid == 0) {
+        if (*a.status != 0) t[4] = -1.0;
+        if (x.world <= 0) {
+            a.result->loss = t[0];
+            a.result->pg_loss = t[1];
+            a.result->kl = t[2];
+            a.result->bad_grads = t[3];
+            a.result->bad_inputs = t[4];
+        }
+#pragma unroll
+        for (int k = 0; k < 5; k++) record[k] = t[k];
+        if (x.world > 0) {
+            // this region's pass number, counted on the device so that a recorded launch can be replayed;
+            // every rank makes the same calls, so the ranks' counters agree
+            unsigned long long* counter = reinterpret_cast<unsigned long long*>(x.peers[x.rank] + kExchangePassOffset);
+            pass_sh = *counter + 1ULL;
+            *counter = pass_sh;
+        }
+    }
+    if (x.world <= 0) return;
+    __syncthreads();
+
+    // ---- the exchange: push, publish, wait, add
+    const unsigned long long seq = pass_sh;
+    const int buf = static_cast<int>(seq & 1ULL);
+    const long long n = 5 + x.n_seq;
+    const long long stride = exchange_stride(x.n_seq);
+    for (int p = 0; p < x.world; p++) {
+        double* dst = exchange_slot(x.peers[p], stride, buf, x.rank);
+        for (long long i = tid; i < n; i += kReduceThreads) dst[i] = i < 5 ? record[i] : x.lengths[i - 5];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < x.world) {
+        unsigned long long* theirs = exchange_flag(x.peers[tid], buf, x.rank);
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(theirs), "l"(seq) : "memory");
+        const unsigned long long* mine = exchange_flag(x.peers[x.rank], buf, tid);
+        const long long start = clock64();
+        for (;;) {
+            unsigned long long seen;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+            if (seen == seq) break;
+            if (clock64() - start > (1LL << 32)) {  // about two seconds: a peer is gone
+                timed_out = 1;
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    double* out = reinterpret_cast<double*>(a.result);
+    for (long long i = tid; i < n; i += kReduceThreads) {
+        double s = 0.0;
+        bool negative = false;
+        for (int q = 0; q < x.world; q++) {
+            const double term = __ldcv(exchange_slot(x.peers[x.rank], stride, buf, q) + i);
+            negative = negative || term < 0.0;
+            s += term;
+        }
+        if (i < 5) {
+            if (i == 4 && negative) s = -1.0;   // some rank's pipeline gave up
+            if (i == 4 && timed_out) s = -2.0;  // some rank never answered
+            out[i] = s;
+        } else {
+            x.lengths[i - 5] = s;
+        }
     }
 }
 
@@ -1023,14 +1108,9 @@ cudaError_t launch_logits_streaming(bool check, const LogitsArgs& a, cudaStream_
     return cudaGetLastError();
 }
 
-cudaError_t launch_logits_terms(const LogitsArgs& a, cudaStream_t stream) {
-    const unsigned blocks = static_cast<unsigned>((a.n_rows + 127) / 128);
-    logits_terms_kernel<<<blocks, 128, 0, stream>>>(a);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_logits_finalize(const LogitsArgs& a, cudaStream_t stream) {
-    logits_finalize_kernel<<<1, 1024, 0, stream>>>(a.rows, a.n_rows, a.status, a.result);
+cudaError_t launch_logits_reduce(const LogitsArgs& a, const ExchangeArgs& x, cudaStream_t stream) {
+    const unsigned blocks = static_cast<unsigned>((a.n_rows + kReduceThreads - 1) / kReduceThreads);
+    logits_reduce_kernel<<<blocks, kReduceThreads, 0, stream>>>(a, x);
     return cudaGetLastError();
 }
 

@@ -164,6 +164,76 @@ def logits(logits_t: torch.Tensor, logp_old, logp_ref, selected, advantages, wei
     return result
 
 
+class PeerExchange:
+    """This rank's exchange region plus the other ranks' regions mapped into this process.
+
+    ``handle`` (64 bytes) is what the ranks trade; ``open_peers`` takes the list of all ranks'
+    handles in rank order.  The region belongs to one :class:`~.sharded.ShardedBoundary`: it counts its
+    passes on the device, and every rank must make the same sequence of calls (``passes`` mirrors the
+    count on the host for bookkeeping only)."""
+
+    def __init__(self, n_seq: int, rank: int, world: int):
+        import ctypes as C
+        if not (1 <= world <= 8 and 0 <= rank < world):
+            raise ValueError("world must lie in [1, 8] and rank in [0, world)")
+        self.n_seq, self.rank, self.world = n_seq, rank, world
+        region = C.c_void_p()
+        _lib.check(_lib.lib().grpo_b200_exchange_create(n_seq, C.byref(region)))
+        self.own = region.value
+        buf = C.create_string_buffer(64)
+        _lib.check(_lib.lib().grpo_b200_exchange_export(self.own, buf))
+        self.handle = buf.raw
+        self.regions = (C.c_void_p * world)()
+        self.regions[rank] = self.own
+        self.passes = 0
+        self._opened = []
+
+    def open_peers(self, handles: list[bytes]) -> None:
+        import ctypes as C
+        if len(handles) != self.world:
+            raise ValueError("one handle per rank, in rank order")
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                continue
+            peer = C.c_void_p()
+            _lib.check(_lib.lib().grpo_b200_exchange_open(C.create_string_buffer(bytes(h), 64), C.byref(peer)))
+            self.regions[r] = peer.value
+            self._opened.append(peer.value)
+
+    def close(self) -> None:
+        for p in self._opened:
+            _lib.lib().grpo_b200_exchange_close(p)
+        self._opened = []
+        if self.own:
+            _lib.lib().grpo_b200_exchange_destroy(self.own)
+            self.own = None
+
+
+def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advantages, weights, mask,
+                   tokens_per_seq: int, V: int, clip_eps: float, beta: float, *, exchange: PeerExchange,
+                   lengths: torch.Tensor, result: torch.Tensor, workspace: torch.Tensor, row_offset: int = 0,
+                   kernel: int = CudaLogitsKernel.fused, check_inputs: bool = False,
+                   selected_logp: torch.Tensor | None = None) -> torch.Tensor:
+    """:func:`logits` in place on this rank's rows, with the sum over ranks of the result record
+    and of ``lengths`` (float64 ``[n_seq]``, in: this rank's partial counts, out: global counts)
+    carried out by the pass's last kernel over the ranks' exchange regions."""
+    n_rows, P = logits_t.shape
+    x = _check_tensor(logits_t, torch.float32, "logits")
+    if lengths.numel() != exchange.n_seq:
+        raise ValueError("lengths must hold one entry per response of the exchange region")
+    exchange.passes += 1
+    _lib.check(_lib.lib().grpo_b200_logits_sharded(
+        x, x, _check_tensor(logp_old, torch.float32, "logp_old"), _check_tensor(logp_ref, torch.float32, "logp_ref"),
+        _check_tensor(selected, torch.int32, "selected"), _check_tensor(advantages, torch.float32, "advantages"),
+        _check_tensor(weights, torch.float32, "weights"), _check_tensor(mask, torch.int32, "mask"),
+        n_rows, row_offset, tokens_per_seq, V, P, float(clip_eps), float(beta), int(kernel), int(check_inputs),
+        None if selected_logp is None else _check_tensor(selected_logp, torch.float32, "selected_logp"),
+        _check_tensor(result, torch.float64, "result"), workspace.data_ptr(), workspace.numel(),
+        exchange.regions, exchange.rank, exchange.world,
+        _check_tensor(lengths, torch.float64, "lengths"), exchange.n_seq, _stream()))
+    return result
+
+
 def set_variant(variant: int) -> None:
     """Force a row-resident kernel variant (index into :func:`variants`), ``-1`` for automatic."""
     _lib.check(_lib.lib().grpo_b200_logits_set_variant(variant))

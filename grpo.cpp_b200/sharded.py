@@ -85,6 +85,7 @@ class ShardedBoundary:
         self.result = self.xchg[:5]
         self.lengths_f64 = self.xchg[5:]
         self.workspace = ops.logits_workspace(self.n_local, device)
+        self.exchange = None  # set by enable_peer_exchange
 
     def _all_reduce(self, t: torch.Tensor) -> None:
         if self.world > 1:
@@ -125,6 +126,37 @@ class ShardedBoundary:
         self.ops.weights_from_lengths_f64(self.lengths_f64, self.reduction, self.alpha, self.weights, self.meta)
         return self.result
 
+    def enable_peer_exchange(self) -> None:
+        """Set up the library's own exchange over NVLink peer memory (CUDA ranks of one box, at most
+        eight): every rank creates its region, the 64-byte handles go round through the process
+        group, every rank maps the others' regions.  Afterwards :meth:`step_peer` needs no
+        collective call at all."""
+        self.exchange = self.ops.PeerExchange(self.S, self.rank, self.world)
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, self.exchange.handle, group=self.group)
+        else:
+            handles[0] = self.exchange.handle
+        self.exchange.open_peers(handles)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody starts a pass before every region is mapped everywhere
+
+    def step_peer(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
+                  next_mask_local=None, kernel: int = CudaLogitsKernel.fused) -> torch.Tensor:
+        """:meth:`step_fused` with the exchange done inside the pass's last kernel instead of by a
+        collective call: three launches per pass (next pass's partial lengths, the row kernel, the
+        reduce-and-exchange kernel) and then the next pass's weights."""
+        nxt = mask_local if next_mask_local is None else next_mask_local
+        if nxt.numel() != self.n_local:
+            raise RuntimeError(f"mask has size {nxt.numel()}, expected {self.n_local}")
+        self.ops.count_lengths_f64(nxt, self.S, self.T, self.row_offset, self.lengths_f64)
+        self.ops.logits_sharded(logits_local, logp_old, logp_ref, selected, advantages, self.weights, mask_local,
+                                self.T, self.V, self.clip_eps, self.beta, exchange=self.exchange,
+                                lengths=self.lengths_f64, result=self.result, workspace=self.workspace,
+                                row_offset=self.row_offset, kernel=kernel)
+        self.ops.weights_from_lengths_f64(self.lengths_f64, self.reduction, self.alpha, self.weights, self.meta)
+        return self.result
+
     def capture(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
                 kernel: int = CudaLogitsKernel.fused):
         """Record one ``step_fused`` pass over these (fixed-address) tensors into a CUDA graph, so that a
@@ -150,6 +182,9 @@ class ShardedBoundary:
         res = self.result.tolist()
         if meta[1] != 0:
             raise RuntimeError("every sequence needs at least one valid token")
+        if res[4] < 0:
+            raise RuntimeError("a pipeline wait timed out on some rank" if res[4] > -2 else
+                               "the exchange between ranks timed out")
         if res[4] != 0:
             raise RuntimeError("selected token is outside the vocabulary")
         loss, pg, kl = (float(torch.tensor(v, dtype=torch.float64).to(torch.float32)) for v in res[:3])

@@ -189,6 +189,39 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
                      int check_inputs, float* selected_logp, grpo_b200_result_t* result,
                      void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream);
 
+/* Token-sharded logits path with the pass's exchange done by the library's own kernel over
+ * NVLink peer memory.  No counterpart in the reference, whose two-GPU demo shards whole
+ * responses and averages on the host (apps/03_two_gpu_train.cu:200-215, 247-281).
+ *
+ * Every rank (one process per GPU of one box, at most 8) owns an exchange region, created here
+ * with cudaMalloc and cleared; it exports a 64-byte inter-process handle, the ranks trade
+ * handles by any means they have, and each opens the others' regions.  regions[world] is a
+ * HOST array of the regions as mapped into this process, regions[rank] being the own one.
+ *
+ * grpo_b200_logits_sharded is grpo_b200_logits on this rank's rows followed, inside the same
+ * last kernel, by the sum over ranks of {the result record, lengths[n_seq]}: on return (in
+ * stream order) result holds the global record and lengths, which came in holding this rank's
+ * partial valid-token counts per response for the next pass (grpo_b200_count_lengths_f64), holds
+ * the global counts, ready for grpo_b200_weights_from_lengths_f64.  The sums are taken in rank
+ * order, so every rank gets the same bits.  The region counts its own passes on the device; the
+ * ranks must make the same sequence of calls on their regions.  A rank whose peers do not answer within about two seconds stops
+ * waiting and reports bad_inputs = -2; nothing blocks forever.  world = 1 runs the same code
+ * against the own region alone. */
+size_t grpo_b200_exchange_bytes(int64_t n_seq);
+int grpo_b200_exchange_create(int64_t n_seq, void** region);
+int grpo_b200_exchange_export(void* region, unsigned char handle[64]);
+int grpo_b200_exchange_open(const unsigned char handle[64], void** peer_region);
+int grpo_b200_exchange_close(void* peer_region);
+int grpo_b200_exchange_destroy(void* region);
+int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* logp_old,
+                             const float* logp_ref, const int32_t* selected,
+                             const float* advantages, const float* weights, const int32_t* mask,
+                             int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P,
+                             float clip_eps, float beta, int kernel, int check_inputs,
+                             float* selected_logp, grpo_b200_result_t* result, void* workspace,
+                             size_t workspace_bytes, void* const* regions, int rank, int world,
+                             double* lengths, int64_t n_seq, grpo_b200_stream_t stream);
+
 /* Tuning hook for benchmarks: force the row-resident kernel variant (index into the table
  * printed by grpo_b200_logits_variant_name), or -1 for the built-in choice.  Process-wide. */
 int grpo_b200_logits_set_variant(int variant);

@@ -74,3 +74,35 @@ def logits(logits_t, logp_old, logp_ref, selected, advantages, weights, mask, to
         x[r, V:] = 0.0
     result.copy_(torch.from_numpy(total))
     return result
+
+
+class PeerExchange:
+    """Stand-in for the device-side exchange region: the sums over ranks that the reduce kernel
+    takes over NVLink are taken by a gloo all-reduce here.  The handle round trip is kept so that
+    ``ShardedBoundary.enable_peer_exchange`` runs unchanged."""
+
+    def __init__(self, n_seq, rank, world):
+        self.n_seq, self.rank, self.world = n_seq, rank, world
+        self.handle = bytes([rank]) * 64
+        self.passes = 0
+        self.peers = None
+
+    def open_peers(self, handles):
+        assert [h[0] for h in handles] == list(range(self.world))
+        self.peers = handles
+
+    def close(self):
+        self.peers = None
+
+
+def logits_sharded(logits_t, logp_old, logp_ref, selected, advantages, weights, mask, tokens_per_seq, V, clip_eps,
+                   beta, *, exchange, lengths, result, workspace, row_offset=0, kernel=1, **_):
+    import torch.distributed as dist
+    assert exchange.peers is not None, "regions must be mapped before the first pass"
+    exchange.passes += 1
+    logits(logits_t, logp_old, logp_ref, selected, advantages, weights, mask, tokens_per_seq, V, clip_eps, beta,
+           row_offset=row_offset, kernel=kernel, result=result)
+    if exchange.world > 1:
+        dist.all_reduce(result)
+        dist.all_reduce(lengths)
+    return result

@@ -331,3 +331,34 @@ def test_fused_exchange_pass_single_rank():
         assert got["valid_tokens"] == want[1]
         assert (np.abs(g3 - want[0]) <= 1e-5 * np.abs(want[0]) + 1e-9).all()
         assert_grad(x.cpu().numpy()[:, : b.V], want[2])
+
+
+@pytest.mark.gpu
+def test_peer_exchange_pass_single_rank():
+    """ShardedBoundary.step_peer at world size 1: the reduce kernel's last block pushes the record
+    and the partial lengths into its own exchange region, publishes and waits on its own sequence
+    number, and adds the one slot -- the whole exchange code path without a second GPU.  Three
+    passes, so that both buffers of the region are reused."""
+    import torch
+    from grpo_cpp_b200.sharded import ShardedBoundary
+    b = W.logits_case(2, 3, 8, 4099, sigma=2.0, min_len=1, reduction=W.LENGTH_WEIGHTED, length_alpha=0.5, seed=32)
+    P = 4100
+    want = run_oracle(b)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    sb = ShardedBoundary(b.S, b.T, b.V, P, clip_eps=b.clip_eps, beta=b.beta, reduction=b.reduction,
+                         length_alpha=b.length_alpha, device=torch.device("cuda"))
+    old, ref, sel, adv, mask = t(b.logp_old), t(b.logp_ref), t(b.selected), t(b.advantages), t(b.mask)
+    sb.prepare(mask)
+    sb.enable_peer_exchange()
+    try:
+        for _ in range(3):
+            x = t(b.padded(P))
+            sb.step_peer(x, old, ref, sel, adv, mask)
+            got = sb.stats()
+            g3 = np.array([got["loss"], got["pg_loss"], got["kl"]])
+            assert got["valid_tokens"] == want[1]
+            assert (np.abs(g3 - want[0]) <= 1e-5 * np.abs(want[0]) + 1e-9).all()
+            assert_grad(x.cpu().numpy()[:, : b.V], want[2])
+            assert sb.lengths_f64.cpu().numpy().astype(np.int64).tolist() == b.mask.reshape(b.S, b.T).sum(1).tolist()
+    finally:
+        sb.exchange.close()

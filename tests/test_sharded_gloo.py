@@ -39,6 +39,7 @@ def _worker(rank, world, port, case, queue):
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
         reduction, alpha, empty_mode = case[:3]
         fused = len(case) > 3 and case[3]
+        peer = fused == "peer"
         b = W.logits_case(2, 3, 5, 33, sigma=2.0, min_len=1, reduction=reduction, length_alpha=alpha, seed=77)
         P = 40
         if empty_mode == "globally_empty":
@@ -56,7 +57,15 @@ def _worker(rank, world, port, case, queue):
         x = torch.from_numpy(b.padded(P)[sl].copy())
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
         sb.prepare(t(b.mask[sl]))
-        if fused:
+        if peer:
+            # as below, through the path whose exchange the last kernel of the pass does itself
+            sb.enable_peer_exchange()
+            scratch = x.clone()
+            sb.step_peer(scratch, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages),
+                         t(b.mask[sl]))
+            sb.step_peer(x, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages), t(b.mask[sl]))
+            assert sb.exchange.passes == 2
+        elif fused:
             # two passes over the batch with one collective each: the second pass runs on the weights
             # that rode along with the first pass's result record
             scratch = x.clone()
@@ -92,7 +101,7 @@ def _worker(rank, world, port, case, queue):
 
 
 @pytest.mark.parametrize("case", [(1, 0.0, None), (2, 0.5, None), (0, 0.0, None), (1, 0.0, None, True),
-                                  (2, 0.5, None, True),
+                                  (2, 0.5, None, True), (1, 0.0, None, "peer"), (2, 1.0, None, "peer"),
                                   (1, 0.0, "empty_on_rank1_only"), (1, 0.0, "globally_empty")])
 def test_two_ranks_over_gloo(case):
     world = 2
