@@ -309,18 +309,20 @@ def gpu_arm(args, spec: dict) -> None:
     # CUDA graph and replayed; an eager loop afterwards times the dominant kernel on its own.
     sampler = ClockSampler(local_rank) if rank == 0 else None
     graph = None
-    # With more than one rank the two collectives stay eager launches: a pass that captured the
-    # NCCL all-reduces in the graph did not complete on this pool (2 ranks), so graphs are used at
-    # one rank only.
+    # --exchange peer: the pass is two launches (row kernel, reduce kernel) and the reduce kernel does the
+    # exchange itself through the ranks' regions (at one rank: its own region).  --exchange nccl: four launches
+    # and one NCCL all-reduce.
+    peer = args.exchange == "peer"
+    if peer:
+        sb.enable_peer_exchange()
+    one_pass = sb.step_peer if peer else sb.step_fused
+    # With more than one rank the pass stays eager launches: a pass that captured NCCL all-reduces in the
+    # graph did not complete on this pool (2 ranks), so graphs are used at one rank only.
     if not args.no_graph and world == 1:
         restore()
         graph = sb.capture(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
 
     sb.prepare(devt["mask"])  # weights for the first pass; every later pass gets them from the pass before
-    peer = world > 1 and args.exchange == "peer"
-    if peer:
-        sb.enable_peer_exchange()
-    one_pass = sb.step_peer if peer else sb.step_fused
 
     def timed_pass(e0, e1):
         e0.record()
@@ -345,15 +347,18 @@ def gpu_arm(args, spec: dict) -> None:
     barrier()
     t_wall = time.perf_counter() - t_wall0
     step_ms = [e0.elapsed_time(e1) for e0, e1 in pairs]
-    kern_ms = []
-    for i in range(3 + min(args.steps, 10)):  # dominant kernel alone (with the reduce kernel behind it)
+    # dominant kernel alone (with the reduce kernel behind it): its own event pair inside an eager pass.  The host
+    # does not wait between iterations, so the launches are queued while the device is still restoring the
+    # logits and the pair brackets device time only, not launch latency.
+    kern_pairs = []
+    for i in range(3 + min(args.steps, 10)):
         restore()
-        barrier()
         e0, e1, k0, k1 = ev(), ev(), ev(), ev()
         device_step(e0, e1, k0, k1)
-        torch.cuda.synchronize()
         if i >= 3:
-            kern_ms.append(k0.elapsed_time(k1))
+            kern_pairs.append((k0, k1))
+    barrier()
+    kern_ms = [k0.elapsed_time(k1) for k0, k1 in kern_pairs]
     stats = sb.stats()  # applies the error contract to the global quantities
 
     total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
@@ -406,8 +411,9 @@ def gpu_arm(args, spec: dict) -> None:
                        "parallelism": f"token-sharded x{world}", "in_place": True, "kernel": plan,
                        "launch": "eager" if graph is None else "one CUDA graph per pass",
                        "sharding": "contiguous row ranges of equal traffic" if world > 1 else "single range",
-                       "exchange": ("none" if world == 1 else "reduce kernel over NVLink peer memory" if peer else
-                                    "one NCCL all-reduce per pass"),
+                       "exchange": ("reduce kernel over NVLink peer memory" if peer and world > 1 else
+                                    "reduce kernel, own region only" if peer else
+                                    "one NCCL all-reduce per pass" if world > 1 else "none"),
                        "l2": "logits restored from a pristine copy and a 256 MB buffer written between passes on "
                              "the same stream, outside the timed event pairs; per-rank logits far exceed the "
                              "126 MB L2"},
@@ -419,8 +425,8 @@ def gpu_arm(args, spec: dict) -> None:
                     "d2h_bytes_per_step": 48, "ms_per_step": 1e3 * e2e_total / args.steps,
                     "api": "grpo_logits_cuda_device_inplace (host metadata, device logits)" if world == 1 else
                            "ShardedBoundary.prepare+step+stats from pinned host metadata"},
-            # per pass and rank: next pass's lengths, the row kernel, the reduce kernel, next pass's weights
-            "gpu_launches": 4 * args.steps * world,
+            # per pass and rank: the row kernel and the reduce kernel (+ lengths and weights kernels with NCCL)
+            "gpu_launches": (2 if peer else 4) * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_kind}",
                          "kernel": f"logits_pipelined_kernel<{plan}> (+ reduce kernel)", "ms_per_launch": k_ms,
@@ -432,10 +438,10 @@ def gpu_arm(args, spec: dict) -> None:
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_single(spec)
         print(json.dumps(line), flush=True)
+    if peer:
+        barrier()  # no rank unmaps a region that another rank's kernel may still write to
+        sb.exchange.close()
     if world > 1:
-        if peer:
-            barrier()  # no rank unmaps a region that another rank's kernel may still write to
-            sb.exchange.close()
         dist.destroy_process_group()
 
 

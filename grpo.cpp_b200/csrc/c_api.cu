@@ -240,7 +240,7 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
 
 size_t grpo_b200_exchange_bytes(int64_t n_seq) {
     if (n_seq <= 0) return 0;
-    return kExchangeHeaderBytes + static_cast<size_t>(2 * kExchangeMaxWorld) * exchange_stride(n_seq) * sizeof(double);
+    return exchange_counts_offset(n_seq) + static_cast<size_t>(n_seq) * sizeof(int32_t);
 }
 
 int grpo_b200_exchange_create(int64_t n_seq, void** region) {
@@ -293,11 +293,18 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                              const int32_t* mask, int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P,
                              float clip_eps, float beta, int kernel, int check_inputs, float* selected_logp,
                              grpo_b200_result_t* result, void* workspace, size_t workspace_bytes,
-                             void* const* regions, int rank, int world, double* lengths, int64_t n_seq,
-                             grpo_b200_stream_t stream) {
+                             void* const* regions, int rank, int world, int64_t n_seq, const int32_t* next_mask,
+                             int reduction, float length_alpha, float* next_weights, int32_t* next_meta,
+                             double* next_lengths, grpo_b200_stream_t stream) {
     if (world < 1 || world > kExchangeMaxWorld) return invalid("world must lie in [1, 8]");
     if (rank < 0 || rank >= world) return invalid("rank must lie in [0, world)");
-    if (!regions || !lengths || n_seq <= 0) return invalid("regions and lengths must not be null and n_seq must be positive");
+    if (!regions || !next_mask || !next_weights || !next_meta || n_seq <= 0)
+        return invalid("regions, next_mask, next_weights and next_meta must not be null and n_seq must be positive");
+    if (reduction < GRPO_B200_SEQUENCE_MEAN || reduction > GRPO_B200_LENGTH_WEIGHTED)
+        return invalid("unknown reduction mode");
+    if (tokens_per_seq > 0 && n_rows > 0 && row_offset >= 0 &&
+        (row_offset + n_rows + tokens_per_seq - 1) / tokens_per_seq > n_seq)
+        return invalid("rows reach beyond the last response");
     ExchangeArgs x = {};
     for (int r = 0; r < world; r++) {
         if (!regions[r]) return invalid("every rank's exchange region must be mapped");
@@ -306,7 +313,12 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
     x.rank = rank;
     x.world = world;
     x.n_seq = n_seq;
-    x.lengths = lengths;
+    x.next_mask = next_mask;
+    x.reduction = reduction;
+    x.length_alpha = length_alpha;
+    x.weights_out = next_weights;
+    x.meta_out = next_meta;
+    x.lengths_out = next_lengths;
     return logits_pass(logits, dlogits, logp_old, logp_ref, selected, advantages, weights, mask, n_rows, row_offset,
                        tokens_per_seq, V, P, clip_eps, beta, kernel, check_inputs, selected_logp, result, workspace,
                        workspace_bytes, x, stream);

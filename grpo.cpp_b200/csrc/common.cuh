@@ -103,6 +103,48 @@ __device__ __forceinline__ void block_sum(double (&v)[NV], double* scratch) {
     }
 }
 
+// Per-response weights and the two counters {valid tokens, empty responses} from global lengths, by
+// one block of THREADS threads: the reference's fp32 expressions (src/cuda/grpo_loss_cuda.cu:43-55).
+// The power is evaluated in double and rounded, which reproduces a correctly rounded powf.
+// `scratch` needs 2 * THREADS/32 + 1 doubles.  Ends with every thread past its last store.
+template <int THREADS, class LEN>
+__device__ __forceinline__ void block_weights(const LEN* lengths, long long n_seq, int reduction, float alpha,
+                                              float* weights, int32_t* meta, double* scratch) {
+    double v[2] = {0.0, 0.0};
+    for (long long s = threadIdx.x; s < n_seq; s += THREADS) {
+        const int L = static_cast<int>(lengths[s]);
+        v[0] += static_cast<double>(L);
+        v[1] += L == 0 ? 1.0 : 0.0;
+    }
+    block_sum<THREADS, 2>(v, scratch);
+    double* total_sh = scratch + 2 * THREADS / 32;
+    if (threadIdx.x == 0) {
+        *total_sh = v[0];
+        meta[0] = static_cast<int32_t>(v[0]);
+        meta[1] = static_cast<int32_t>(v[1]);
+    }
+    __syncthreads();
+    const float n_valid = static_cast<float>(static_cast<int32_t>(*total_sh));
+    const float n_seq_f = static_cast<float>(n_seq);
+    const float expo = __fsub_rn(alpha, 1.0f);
+    for (long long s = threadIdx.x; s < n_seq; s += THREADS) {
+        const int L = static_cast<int>(lengths[s]);
+        float w = 0.0f;
+        if (L > 0) {
+            const float Lf = static_cast<float>(L);
+            if (reduction == GRPO_B200_SEQUENCE_MEAN) {
+                w = __fdiv_rn(1.0f, __fmul_rn(n_seq_f, Lf));
+            } else if (reduction == GRPO_B200_TOKEN_MEAN) {
+                w = __fdiv_rn(1.0f, n_valid);
+            } else {
+                const float p = static_cast<float>(pow(static_cast<double>(Lf), static_cast<double>(expo)));
+                w = __fdiv_rn(p, n_seq_f);
+            }
+        }
+        weights[s] = w;
+    }
+}
+
 // base-2 exponential on the special-function unit (max relative error about 2^-22)
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -170,19 +212,28 @@ struct LogitsArgs {
 };
 
 // The exchange region of one rank (device memory that every rank of the box maps): a header of
-// sequence numbers flags[2][8] and the region's own pass counter, then slots[2][8][stride] doubles;
-// [buffer = pass & 1][source rank].
+// sequence numbers flags[2][8] and the region's own pass counter, then slots[2][8][stride] doubles
+// ([buffer = pass & 1][source rank]), then counts[n_seq] int32, this rank's valid-token counts for
+// the next pass (zero between passes: the kernel that reads them clears them).
 constexpr int kExchangeMaxWorld = 8;
 constexpr int kExchangePassOffset = 128;
 constexpr int kExchangeHeaderBytes = 256;
 __host__ __device__ inline long long exchange_stride(long long n_seq) { return (5 + n_seq + 1) & ~1LL; }
+__host__ __device__ inline size_t exchange_counts_offset(long long n_seq) {
+    return kExchangeHeaderBytes + static_cast<size_t>(2 * kExchangeMaxWorld) * exchange_stride(n_seq) * sizeof(double);
+}
 
 struct ExchangeArgs {
     unsigned char* peers[kExchangeMaxWorld];  // every rank's region as mapped into this process; [rank] is this GPU's own
     int rank;
     int world;  // 0: no exchange, the record goes straight to `result`
     long long n_seq;
-    double* lengths;  // [n_seq] in: this rank's partial response lengths; out: their sums over ranks
+    const int32_t* next_mask;  // [n_rows] the next pass's mask over the same rows (may be this pass's)
+    int reduction;
+    float length_alpha;
+    float* weights_out;  // [n_seq] the next pass's weights
+    int32_t* meta_out;   // {valid tokens, empty responses} of the next pass's mask
+    double* lengths_out; // [n_seq] global valid-token counts of the next pass's mask (nullable)
 };
 // flags stored in row_terms.w (small integers, exact in fp32)
 constexpr float kRowBadGrad = 1.0f;

@@ -824,15 +824,18 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
 //
 // 1. One thread per row redoes the row's scalar step in double -- log-sum-exp, log p(selected)
 //    rounded to fp32 exactly as the reference rounds it, the two exponentials -- and each block of
-//    256 rows leaves its five sums (fixed tree) in its own slot of the workspace.
+//    256 rows leaves its five sums (fixed tree) in its own slot of the workspace.  Sharded runs:
+//    the same threads count the next pass's valid tokens per response (integer atomics: exact,
+//    so order does not matter) into the rank's exchange region.
 // 2. The block that finishes last (a ticket counter; no floating-point atomics anywhere) adds the
 //    slots in index order, so the totals depend on the row count only, never on scheduling.
 // 3. Sharded runs: the same block then carries out the pass's only exchange itself.  It writes
-//    the record, followed by this rank's partial response lengths for the next pass, into its
-//    slot of every rank's exchange region over NVLink, publishes a per-slot sequence number with
-//    a system-scope release, waits (bounded) for the other ranks' numbers, and adds the slots in
-//    rank order -- the same bits on every rank.  A non-zero status word (a pipeline wait timed
-//    out) turns bad_inputs into -1, an exchange that timed out into -2.
+//    the record, followed by this rank's counts, into its slot of every rank's exchange region
+//    over NVLink, publishes a per-slot sequence number with a system-scope release, waits
+//    (bounded) for the other ranks' numbers, adds the slots in rank order -- the same bits on
+//    every rank -- and derives the next pass's weights from the global counts.  A non-zero
+//    status word (a pipeline wait timed out) turns bad_inputs into -1, an exchange that timed
+//    out into -2.
 constexpr int kReduceThreads = 256;
 
 __device__ __forceinline__ unsigned long long* exchange_flag(unsigned char* region, int buf, int src) {
@@ -845,10 +848,27 @@ __device__ __forceinline__ double* exchange_slot(unsigned char* region, long lon
 __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const LogitsArgs a, const ExchangeArgs x) {
     __shared__ double scratch[5 * kReduceThreads / 32];
     __shared__ double record[5];
+    __shared__ int hist[kReduceThreads + 1];
     __shared__ int is_last, timed_out;
     __shared__ unsigned long long pass_sh;
     const int tid = threadIdx.x;
-    const long long row = static_cast<long long>(blockIdx.x) * kReduceThreads + tid;
+    const long long first_row = static_cast<long long>(blockIdx.x) * kReduceThreads;
+    const long long row = first_row + tid;
+
+    // ---- the next pass's valid tokens per response among this block's rows
+    if (x.world > 0) {
+        const long long first_seq = (a.row_offset + first_row) / a.tokens_per_seq;
+        hist[tid] = 0;
+        if (tid == 0) hist[kReduceThreads] = 0;
+        __syncthreads();
+        if (row < a.n_rows && x.next_mask[row] != 0)
+            atomicAdd(&hist[static_cast<int>((a.row_offset + row) / a.tokens_per_seq - first_seq)], 1);
+        __syncthreads();
+        int32_t* counts = reinterpret_cast<int32_t*>(x.peers[x.rank] + exchange_counts_offset(x.n_seq));
+        for (int i = tid; i <= kReduceThreads; i += kReduceThreads)
+            if (hist[i] != 0) atomicAdd(counts + first_seq + i, hist[i]);
+    }
+
     double v[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
     if (row < a.n_rows) {
         float lp_new = 0.0f;
@@ -870,7 +890,7 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
     if (tid == 0) {
 #pragma unroll
         for (int k = 0; k < 5; k++) a.partials[static_cast<size_t>(blockIdx.x) * 5 + k] = v[k];
-        __threadfence();
+        __threadfence();  // the slot and this block's counts are visible before the ticket is taken
         is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
         timed_out = 0;
     }
@@ -906,14 +926,21 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
     if (x.world <= 0) return;
     __syncthreads();
 
-    // ---- the exchange: push, publish, wait, add
+    // ---- the exchange: push (clearing the counts for the next pass), publish, wait, add
     const unsigned long long seq = pass_sh;
     const int buf = static_cast<int>(seq & 1ULL);
     const long long n = 5 + x.n_seq;
     const long long stride = exchange_stride(x.n_seq);
-    for (int p = 0; p < x.world; p++) {
-        double* dst = exchange_slot(x.peers[p], stride, buf, x.rank);
-        for (long long i = tid; i < n; i += kReduceThreads) dst[i] = i < 5 ? record[i] : x.lengths[i - 5];
+    int32_t* counts = reinterpret_cast<int32_t*>(x.peers[x.rank] + exchange_counts_offset(x.n_seq));
+    for (long long i = tid; i < n; i += kReduceThreads) {
+        double mine = 0.0;
+        if (i < 5) {
+            mine = record[i];
+        } else {
+            mine = static_cast<double>(__ldcg(counts + (i - 5)));
+            counts[i - 5] = 0;
+        }
+        for (int p = 0; p < x.world; p++) exchange_slot(x.peers[p], stride, buf, x.rank)[i] = mine;
     }
     __threadfence_system();
     __syncthreads();
@@ -934,7 +961,10 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
         }
     }
     __syncthreads();
+    // the global counts are written over this rank's own slot of this buffer (thread i is the only reader of
+    // element i, and nobody else writes the slot), where the weights step below reads them
     double* out = reinterpret_cast<double*>(a.result);
+    double* global_lengths = exchange_slot(x.peers[x.rank], stride, buf, x.rank) + 5;
     for (long long i = tid; i < n; i += kReduceThreads) {
         double s = 0.0;
         bool negative = false;
@@ -948,9 +978,13 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
             if (i == 4 && timed_out) s = -2.0;  // some rank never answered
             out[i] = s;
         } else {
-            x.lengths[i - 5] = s;
+            global_lengths[i - 5] = s;
+            if (x.lengths_out) x.lengths_out[i - 5] = s;
         }
     }
+    __syncthreads();
+    block_weights<kReduceThreads>(global_lengths, x.n_seq, x.reduction, x.length_alpha, x.weights_out, x.meta_out,
+                                  scratch);
 }
 
 // ---- variant table of the pipelined kernel --------------------------------------------------------

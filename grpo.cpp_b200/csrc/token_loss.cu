@@ -148,40 +148,8 @@ template <class LEN>
 __global__ void __launch_bounds__(1024) weights_kernel(const LEN* __restrict__ lengths, long long n_seq,
                                                        int reduction, float alpha, float* __restrict__ weights,
                                                        int32_t* __restrict__ meta) {
-    __shared__ double scratch[2 * 1024 / 32];
-    __shared__ double total_sh;
-    double v[2] = {0.0, 0.0};
-    for (long long s = threadIdx.x; s < n_seq; s += 1024) {
-        const int L = static_cast<int>(lengths[s]);
-        v[0] += static_cast<double>(L);
-        v[1] += L == 0 ? 1.0 : 0.0;
-    }
-    block_sum<1024, 2>(v, scratch);
-    if (threadIdx.x == 0) {
-        total_sh = v[0];
-        meta[0] = static_cast<int32_t>(v[0]);
-        meta[1] = static_cast<int32_t>(v[1]);
-    }
-    __syncthreads();
-    const float n_valid = static_cast<float>(static_cast<int32_t>(total_sh));
-    const float n_seq_f = static_cast<float>(n_seq);
-    const float expo = __fsub_rn(alpha, 1.0f);
-    for (long long s = threadIdx.x; s < n_seq; s += 1024) {
-        const int L = static_cast<int>(lengths[s]);
-        float w = 0.0f;
-        if (L > 0) {
-            const float Lf = static_cast<float>(L);
-            if (reduction == GRPO_B200_SEQUENCE_MEAN) {
-                w = __fdiv_rn(1.0f, __fmul_rn(n_seq_f, Lf));
-            } else if (reduction == GRPO_B200_TOKEN_MEAN) {
-                w = __fdiv_rn(1.0f, n_valid);
-            } else {
-                const float p = static_cast<float>(pow(static_cast<double>(Lf), static_cast<double>(expo)));
-                w = __fdiv_rn(p, n_seq_f);
-            }
-        }
-        weights[s] = w;
-    }
+    __shared__ double scratch[2 * 1024 / 32 + 1];
+    block_weights<1024>(lengths, n_seq, reduction, alpha, weights, meta, scratch);
 }
 
 // One thread per prompt walks its G rewards in order: Welford mean / M2 in double with

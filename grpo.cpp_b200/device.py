@@ -211,16 +211,21 @@ class PeerExchange:
 
 def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advantages, weights, mask,
                    tokens_per_seq: int, V: int, clip_eps: float, beta: float, *, exchange: PeerExchange,
-                   lengths: torch.Tensor, result: torch.Tensor, workspace: torch.Tensor, row_offset: int = 0,
+                   next_mask: torch.Tensor, reduction: int, length_alpha: float, next_weights: torch.Tensor,
+                   next_meta: torch.Tensor, result: torch.Tensor, workspace: torch.Tensor,
+                   next_lengths: torch.Tensor | None = None, row_offset: int = 0,
                    kernel: int = CudaLogitsKernel.fused, check_inputs: bool = False,
                    selected_logp: torch.Tensor | None = None) -> torch.Tensor:
-    """:func:`logits` in place on this rank's rows, with the sum over ranks of the result record
-    and of ``lengths`` (float64 ``[n_seq]``, in: this rank's partial counts, out: global counts)
-    carried out by the pass's last kernel over the ranks' exchange regions."""
+    """:func:`logits` in place on this rank's rows; the pass's last kernel also counts ``next_mask``'s
+    valid tokens, sums the result record and the counts over the ranks through their exchange
+    regions, and writes the next pass's weights (``next_weights`` may be ``weights``) and
+    ``next_meta = [valid_tokens, empty_responses]``."""
     n_rows, P = logits_t.shape
     x = _check_tensor(logits_t, torch.float32, "logits")
-    if lengths.numel() != exchange.n_seq:
-        raise ValueError("lengths must hold one entry per response of the exchange region")
+    if next_mask.numel() != n_rows:
+        raise ValueError("next_mask must cover the same rows as mask")
+    if next_weights.numel() != exchange.n_seq:
+        raise ValueError("next_weights must hold one entry per response of the exchange region")
     exchange.passes += 1
     _lib.check(_lib.lib().grpo_b200_logits_sharded(
         x, x, _check_tensor(logp_old, torch.float32, "logp_old"), _check_tensor(logp_ref, torch.float32, "logp_ref"),
@@ -229,8 +234,10 @@ def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advanta
         n_rows, row_offset, tokens_per_seq, V, P, float(clip_eps), float(beta), int(kernel), int(check_inputs),
         None if selected_logp is None else _check_tensor(selected_logp, torch.float32, "selected_logp"),
         _check_tensor(result, torch.float64, "result"), workspace.data_ptr(), workspace.numel(),
-        exchange.regions, exchange.rank, exchange.world,
-        _check_tensor(lengths, torch.float64, "lengths"), exchange.n_seq, _stream()))
+        exchange.regions, exchange.rank, exchange.world, exchange.n_seq,
+        _check_tensor(next_mask, torch.int32, "next_mask"), int(reduction), float(length_alpha),
+        _check_tensor(next_weights, torch.float32, "next_weights"), _check_tensor(next_meta, torch.int32, "next_meta"),
+        None if next_lengths is None else _check_tensor(next_lengths, torch.float64, "next_lengths"), _stream()))
     return result
 
 

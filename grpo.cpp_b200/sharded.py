@@ -143,36 +143,37 @@ class ShardedBoundary:
 
     def step_peer(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
                   next_mask_local=None, kernel: int = CudaLogitsKernel.fused) -> torch.Tensor:
-        """:meth:`step_fused` with the exchange done inside the pass's last kernel instead of by a
-        collective call: three launches per pass (next pass's partial lengths, the row kernel, the
-        reduce-and-exchange kernel) and then the next pass's weights."""
+        """:meth:`step_fused` without a collective call and with two launches per pass: the row
+        kernel, then the reduce kernel, which also counts the next mask's valid tokens, exchanges
+        them together with the result record through the ranks' regions, and writes the next
+        pass's weights.  Works at world size 1 too (the region is then this rank's alone)."""
         nxt = mask_local if next_mask_local is None else next_mask_local
         if nxt.numel() != self.n_local:
             raise RuntimeError(f"mask has size {nxt.numel()}, expected {self.n_local}")
-        self.ops.count_lengths_f64(nxt, self.S, self.T, self.row_offset, self.lengths_f64)
         self.ops.logits_sharded(logits_local, logp_old, logp_ref, selected, advantages, self.weights, mask_local,
-                                self.T, self.V, self.clip_eps, self.beta, exchange=self.exchange,
-                                lengths=self.lengths_f64, result=self.result, workspace=self.workspace,
-                                row_offset=self.row_offset, kernel=kernel)
-        self.ops.weights_from_lengths_f64(self.lengths_f64, self.reduction, self.alpha, self.weights, self.meta)
+                                self.T, self.V, self.clip_eps, self.beta, exchange=self.exchange, next_mask=nxt,
+                                reduction=self.reduction, length_alpha=self.alpha, next_weights=self.weights,
+                                next_meta=self.meta, next_lengths=self.lengths_f64, result=self.result,
+                                workspace=self.workspace, row_offset=self.row_offset, kernel=kernel)
         return self.result
 
     def capture(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
                 kernel: int = CudaLogitsKernel.fused):
-        """Record one ``step_fused`` pass over these (fixed-address) tensors into a CUDA graph, so that a
+        """Record one pass (``step_peer`` when the exchange is enabled, else ``step_fused``) over these (fixed-address) tensors into a CUDA graph, so that a
         pass is one graph launch and its small launches do not wait on host dispatch.
         One eager pass runs first (kernel attributes, occupancy queries and NCCL set-up must not
         happen under capture); it consumes the logits in place like any pass."""
+        one_pass = self.step_peer if self.exchange is not None else self.step_fused
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             self.prepare(mask_local)
-            self.step_fused(logits_local, logp_old, logp_ref, selected, advantages, mask_local, None, kernel)
+            one_pass(logits_local, logp_old, logp_ref, selected, advantages, mask_local, None, kernel)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self.step_fused(logits_local, logp_old, logp_ref, selected, advantages, mask_local, None, kernel)
+            one_pass(logits_local, logp_old, logp_ref, selected, advantages, mask_local, None, kernel)
         return graph
 
     def stats(self) -> dict:

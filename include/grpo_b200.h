@@ -199,12 +199,15 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
  * HOST array of the regions as mapped into this process, regions[rank] being the own one.
  *
  * grpo_b200_logits_sharded is grpo_b200_logits on this rank's rows followed, inside the same
- * last kernel, by the sum over ranks of {the result record, lengths[n_seq]}: on return (in
- * stream order) result holds the global record and lengths, which came in holding this rank's
- * partial valid-token counts per response for the next pass (grpo_b200_count_lengths_f64), holds
- * the global counts, ready for grpo_b200_weights_from_lengths_f64.  The sums are taken in rank
- * order, so every rank gets the same bits.  The region counts its own passes on the device; the
- * ranks must make the same sequence of calls on their regions.  A rank whose peers do not answer within about two seconds stops
+ * last kernel, by everything the ranks must agree on: it counts next_mask's valid tokens per
+ * response among this rank's rows (next_mask may be mask itself), sums {the result record, the
+ * counts} over the ranks, and derives the next pass's weights from the global counts.  On
+ * return (in stream order) result holds the global record, next_weights[n_seq] and
+ * next_meta[2] what grpo_b200_weights_from_lengths would give for the whole batch's next_mask
+ * (next_weights may be the buffer `weights` points to), and next_lengths[n_seq] (nullable) the
+ * global counts as doubles.  The sums are taken in rank order, so every rank gets the same
+ * bits.  The region counts its own passes on the device; the ranks must make the same sequence
+ * of calls on their regions.  A rank whose peers do not answer within about two seconds stops
  * waiting and reports bad_inputs = -2; nothing blocks forever.  world = 1 runs the same code
  * against the own region alone. */
 size_t grpo_b200_exchange_bytes(int64_t n_seq);
@@ -220,7 +223,9 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                              float clip_eps, float beta, int kernel, int check_inputs,
                              float* selected_logp, grpo_b200_result_t* result, void* workspace,
                              size_t workspace_bytes, void* const* regions, int rank, int world,
-                             double* lengths, int64_t n_seq, grpo_b200_stream_t stream);
+                             int64_t n_seq, const int32_t* next_mask, int reduction,
+                             float length_alpha, float* next_weights, int32_t* next_meta,
+                             double* next_lengths, grpo_b200_stream_t stream);
 
 /* Tuning hook for benchmarks: force the row-resident kernel variant (index into the table
  * printed by grpo_b200_logits_variant_name), or -1 for the built-in choice.  Process-wide. */

@@ -96,13 +96,18 @@ class PeerExchange:
 
 
 def logits_sharded(logits_t, logp_old, logp_ref, selected, advantages, weights, mask, tokens_per_seq, V, clip_eps,
-                   beta, *, exchange, lengths, result, workspace, row_offset=0, kernel=1, **_):
+                   beta, *, exchange, next_mask, reduction, length_alpha, next_weights, next_meta, result, workspace,
+                   next_lengths=None, row_offset=0, kernel=1, **_):
     import torch.distributed as dist
     assert exchange.peers is not None, "regions must be mapped before the first pass"
     exchange.passes += 1
     logits(logits_t, logp_old, logp_ref, selected, advantages, weights, mask, tokens_per_seq, V, clip_eps, beta,
            row_offset=row_offset, kernel=kernel, result=result)
+    counts = count_lengths(next_mask, exchange.n_seq, tokens_per_seq, row_offset).to(torch.float64)
     if exchange.world > 1:
         dist.all_reduce(result)
-        dist.all_reduce(lengths)
+        dist.all_reduce(counts)
+    if next_lengths is not None:
+        next_lengths.copy_(counts)
+    weights_from_lengths(counts.to(torch.int32), reduction, length_alpha, next_weights, next_meta)
     return result
