@@ -121,7 +121,7 @@ int grpo_b200_group_advantages(const float* rewards, int B, int G, int mode, flo
 
 size_t grpo_b200_loss_workspace_bytes(int64_t n_tokens) {
     (void)n_tokens;
-    return static_cast<size_t>(2048) * 5 * sizeof(double);  // per-block partials, fixed upper bound
+    return static_cast<size_t>(2048) * 5 * sizeof(double) + 8;  // per-block partials (fixed upper bound) + ticket counter
 }
 
 int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* logp_ref, const float* advantages,
@@ -153,6 +153,7 @@ int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* lo
     a.dlogp = dlogp;
     a.result = result;
     a.partials = static_cast<double*>(workspace);
+    a.counter = reinterpret_cast<unsigned*>(a.partials + 2048 * 5);
     GRPO_CUDA_TRY(launch_loss(a, reinterpret_cast<cudaStream_t>(stream)));
     return GRPO_B200_OK;
 }
@@ -213,7 +214,6 @@ int logits_pass(const float* logits, float* dlogits, const float* logp_old, cons
     a.counter = reinterpret_cast<unsigned*>(a.status) + 1;
     a.partials = reinterpret_cast<double*>(reinterpret_cast<unsigned char*>(a.status) + 32);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    GRPO_CUDA_TRY(cudaMemsetAsync(a.status, 0, 32, s));
     const int variant = kernel == GRPO_B200_LOGITS_FUSED ? pick_resident_variant(logits, dlogits, V, P) : -1;
     if (variant >= 0)
         GRPO_CUDA_TRY(launch_logits_resident(variant, check_inputs != 0, a, s));

@@ -173,7 +173,8 @@ struct LossArgs {
     float clip_eps, beta;
     float* dlogp;
     grpo_b200_result_t* result;
-    double* partials;  // [blocks][4]
+    double* partials;   // [blocks][5]
+    unsigned* counter;  // ticket counter of the blocks (cleared before the launch); unused by the two-launch form
 };
 int loss_grid_blocks(long long n_tokens);
 cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream);

@@ -342,6 +342,13 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const bool is_producer = warp == WARPS;
+    // The pass's control words start from zero without a separate clearing launch: block 0 is
+    // resident from the first instant (the grid never exceeds what fits at once), a wait gives up
+    // only after seconds, and the reduce kernel that reads them runs after this kernel.
+    if (blockIdx.x == 0 && tid == 0) {
+        *a.status = 0;
+        *a.counter = 0u;
+    }
     unsigned crank = 0;
     if (CLUSTER > 1) crank = cg::this_cluster().block_rank();
     const int cluster_id = blockIdx.x / CLUSTER;
@@ -395,10 +402,54 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     if (blockIdx.x == 0 && threadIdx.x == 0) g_timeline_grid = static_cast<int>(gridDim.x);
 #endif
 
-    for (int batch_first = 0; batch_first < n_mine; batch_first += BATCH) {
+    if (is_producer) {
+        // ---- producer warp: free-running over all of this cluster's rows.  The lanes read 32 rows'
+        //      mask words at a time (one group ahead, so the latency hides behind the group being
+        //      issued); lane 0 requests every tile of every active row, in order, as the ring's
+        //      stages come free.  It shares nothing with the consumers but the ring.
+        if (n_tiles > 0) {
+            auto group_mask = [&](int base) -> unsigned {
+                const int k = base + lane;
+                int mk = 0;
+                if (k < n_mine) mk = a.mask[static_cast<size_t>(cluster_id) + static_cast<size_t>(k) * n_clusters] != 0;
+                return __ballot_sync(0xffffffffu, mk);
+            };
+            unsigned next_bits = group_mask(0);
+            for (int base = 0; base < n_mine && alive; base += 32) {
+                unsigned bits = next_bits;
+                if (base + 32 < n_mine) next_bits = group_mask(base + 32);
+                if (lane == 0) {
+                    while (bits != 0 && alive) {
+                        const int k_row = base + __ffs(bits) - 1;
+                        bits &= bits - 1;
+                        const size_t p_row = static_cast<size_t>(cluster_id) + static_cast<size_t>(k_row) * n_clusters;
+                        const float* row_src = a.logits + p_row * static_cast<size_t>(a.P) + 4 * static_cast<size_t>(c0);
+                        for (int t = 0; t < n_tiles; t++) {
+                            const unsigned slot = q % STAGES;
+                            const unsigned parity = (q / STAGES) & 1u;
+                            if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
+                                alive = false;
+                                abort_sh = 1;
+                                break;
+                            }
+                            const int first = t * TILE_CHUNKS;
+                            const uint32_t bytes = static_cast<uint32_t>(min(TILE_CHUNKS, n_load - first)) * 16u;
+                            mbar_arrive_expect_tx(&full_bar[slot], bytes);
+                            bulk_load(ring + static_cast<size_t>(slot) * TILE_CHUNKS,
+                                      row_src + 4 * static_cast<size_t>(first), bytes, &full_bar[slot]);
+                            q++;
+                        }
+                    }
+                }
+                alive = __shfl_sync(0xffffffffu, static_cast<int>(alive), 0) != 0;  // the loop condition stays uniform
+            }
+        }
+    }
+
+    for (int batch_first = 0; !is_producer && batch_first < n_mine; batch_first += BATCH) {
         const int batch_rows = min(BATCH, n_mine - batch_first);
-        __syncthreads();  // everyone, producer included, is done with the previous batch's scalars
-        for (int i = tid; i < batch_rows; i += THREADS + 32) {
+        consumer_sync(THREADS);  // every consumer is done with the previous batch's scalars
+        for (int i = tid; i < batch_rows; i += THREADS) {
             const size_t r = static_cast<size_t>(cluster_id) + static_cast<size_t>(batch_first + i) * n_clusters;
             const int mk = a.mask[r];
             meta_mask[i] = mk != 0;
@@ -411,36 +462,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                 meta_w[i] = a.weights[seq];
             }
         }
-        __syncthreads();
-
-        if (is_producer) {
-            // ---- producer warp: one lane requests every tile of every active row of the batch, in
-            //      order, as the ring's stages come free
-            if (lane == 0 && n_tiles > 0) {
-                for (int k_row = 0; k_row < batch_rows && alive; k_row++) {
-                    if (meta_mask[k_row] == 0) continue;
-                    const size_t p_row =
-                        static_cast<size_t>(cluster_id) + static_cast<size_t>(batch_first + k_row) * n_clusters;
-                    const float* row_src = a.logits + p_row * static_cast<size_t>(a.P) + 4 * static_cast<size_t>(c0);
-                    for (int t = 0; t < n_tiles; t++) {
-                        const unsigned slot = q % STAGES;
-                        const unsigned parity = (q / STAGES) & 1u;
-                        if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
-                            alive = false;
-                            abort_sh = 1;
-                            break;
-                        }
-                        const int first = t * TILE_CHUNKS;
-                        const uint32_t bytes = static_cast<uint32_t>(min(TILE_CHUNKS, n_load - first)) * 16u;
-                        mbar_arrive_expect_tx(&full_bar[slot], bytes);
-                        bulk_load(ring + static_cast<size_t>(slot) * TILE_CHUNKS, row_src + 4 * static_cast<size_t>(first),
-                                  bytes, &full_bar[slot]);
-                        q++;
-                    }
-                }
-            }
-            continue;  // next batch
-        }
+        consumer_sync(THREADS);
 
         // ---- consumer warps
         for (int k_row = 0; k_row < batch_rows; k_row++) {
@@ -731,6 +753,12 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
     const float* in = a.logits + row * static_cast<long long>(a.P);
     float* out = a.dlogits + row * static_cast<long long>(a.P);
     const int V = a.V, P = a.P;
+    // the pass's control words start from zero (this kernel never sets the status word; the reduce
+    // kernel, which runs after it, reads both)
+    if (blockIdx.x == 0 && tid == 0) {
+        *a.status = 0;
+        *a.counter = 0u;
+    }
 
     if (a.mask[row] == 0) {
         for (int v = tid; v < P; v += kStreamThreads) out[v] = 0.0f;

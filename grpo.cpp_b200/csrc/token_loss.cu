@@ -40,15 +40,18 @@ __device__ __forceinline__ float one_token(const LossArgs& a, float lp_new, floa
     return t.grad;
 }
 
-template <bool VEC>
-__global__ void __launch_bounds__(kLossThreads) token_loss_kernel(const LossArgs a) {
-    __shared__ double scratch[kPartialWidth * kLossThreads / 32];
+// TICKET: the block that takes the last ticket also adds the per-block partials in index order and
+// writes the result record, so the pass is one kernel launch (after a 4-byte clear of the counter).
+template <bool VEC, int THREADS, bool TICKET>
+__global__ void __launch_bounds__(THREADS) token_loss_kernel(const LossArgs a) {
+    __shared__ double scratch[kPartialWidth * THREADS / 32];
+    __shared__ int is_last;
     Acc acc;
 #pragma unroll
     for (int k = 0; k < kPartialWidth; k++) acc.v[k] = 0.0;
 
-    const long long tid = static_cast<long long>(blockIdx.x) * kLossThreads + threadIdx.x;
-    const long long stride = static_cast<long long>(gridDim.x) * kLossThreads;
+    const long long tid = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * THREADS;
     const long long T = a.tokens_per_seq;
 
     if (VEC) {
@@ -94,10 +97,33 @@ __global__ void __launch_bounds__(kLossThreads) token_loss_kernel(const LossArgs
         }
     }
 
-    block_sum<kLossThreads, kPartialWidth>(acc.v, scratch);
+    block_sum<THREADS, kPartialWidth>(acc.v, scratch);
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int k = 0; k < kPartialWidth; k++) a.partials[blockIdx.x * kPartialWidth + k] = acc.v[k];
+        if (TICKET) {
+            __threadfence();
+            is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+        }
+    }
+    if (!TICKET) return;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    double v[kPartialWidth];
+#pragma unroll
+    for (int k = 0; k < kPartialWidth; k++) v[k] = 0.0;
+    for (unsigned b = threadIdx.x; b < gridDim.x; b += THREADS) {
+#pragma unroll
+        for (int k = 0; k < kPartialWidth; k++) v[k] += __ldcg(a.partials + b * kPartialWidth + k);
+    }
+    block_sum<THREADS, kPartialWidth>(v, scratch);
+    if (threadIdx.x == 0) {
+        a.result->loss = v[0];
+        a.result->pg_loss = v[1];
+        a.result->kl = v[2];
+        a.result->bad_grads = v[3];
+        a.result->bad_inputs = v[4];
     }
 }
 
@@ -214,16 +240,15 @@ int loss_grid_blocks(long long n_tokens) {
 }
 
 cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream) {
-    const int blocks = loss_grid_blocks(a.n_tokens);
     const bool vec = aligned16(a.logp_new) && aligned16(a.logp_old) && aligned16(a.logp_ref) &&
                      aligned16(a.mask) && aligned16(a.dlogp);
-    if (vec)
-        token_loss_kernel<true><<<blocks, kLossThreads, 0, stream>>>(a);
-    else
-        token_loss_kernel<false><<<blocks, kLossThreads, 0, stream>>>(a);
-    cudaError_t err = cudaGetLastError();
+    const int blocks = loss_grid_blocks(a.n_tokens);
+    cudaError_t err = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), stream);
     if (err != cudaSuccess) return err;
-    loss_finalize_kernel<<<1, 256, 0, stream>>>(a.partials, blocks, a.result);
+    if (vec)
+        token_loss_kernel<true, kLossThreads, true><<<blocks, kLossThreads, 0, stream>>>(a);
+    else
+        token_loss_kernel<false, kLossThreads, true><<<blocks, kLossThreads, 0, stream>>>(a);
     return cudaGetLastError();
 }
 
@@ -351,6 +376,7 @@ extern "C" int grpo_b200_loss_noalloc(const float* logp_new, const float* logp_o
     a.dlogp = dlogp;
     a.result = result;
     a.partials = scratch;
+    a.counter = nullptr;  // two-launch form: no ticket
 
     // Same kernels as grpo_b200_loss, with the grid capped at the number of partial slots held here.
     // Every block overwrites its own slot and the finalize pass reads exactly `blocks` slots, so
@@ -361,9 +387,9 @@ extern "C" int grpo_b200_loss_noalloc(const float* logp_new, const float* logp_o
     const bool vec = aligned16(logp_new) && aligned16(logp_old) && aligned16(logp_ref) && aligned16(mask) &&
                      aligned16(dlogp);
     if (vec)
-        token_loss_kernel<true><<<blocks, kLossThreads, 0, s>>>(a);
+        token_loss_kernel<true, kLossThreads, false><<<blocks, kLossThreads, 0, s>>>(a);
     else
-        token_loss_kernel<false><<<blocks, kLossThreads, 0, s>>>(a);
+        token_loss_kernel<false, kLossThreads, false><<<blocks, kLossThreads, 0, s>>>(a);
     GRPO_CUDA_TRY(cudaGetLastError());
     loss_finalize_kernel<<<1, 256, 0, s>>>(scratch, blocks, result);
     GRPO_CUDA_TRY(cudaGetLastError());
