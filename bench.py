@@ -250,7 +250,7 @@ def gpu_arm(args, spec: dict) -> None:
     B, Gn, T, V, P = spec["B"], spec["G"], spec["T"], spec["V"], spec["P"]
     S, N = B * Gn, B * Gn * T
     mask_h, sel_h, adv_h, noise_old, noise_ref = host_metadata(spec)
-    # contiguous row ranges of equal traffic (ragged masks make equal row counts unequal work)
+    # contiguous row ranges of equal kernel time (ragged masks make equal row counts unequal work)
     off, cnt = shard_rows_balanced(mask_h, world, V, P)[rank]
     sl = slice(off, off + cnt)
 
@@ -299,7 +299,8 @@ def gpu_arm(args, spec: dict) -> None:
         sb.prepare(devt["mask"])
         k0.record()
         sb.ops.logits(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], sb.weights, devt["mask"], T, V,
-                      CLIP_EPS, BETA, row_offset=sb.row_offset, result=sb.result, workspace=sb.workspace)
+                      CLIP_EPS, BETA, row_offset=sb.row_offset, result=sb.result, workspace=sb.workspace,
+                      row_order=sb.row_order)
         k1.record()
         sb._all_reduce(sb.result)
         e1.record()
@@ -410,7 +411,7 @@ def gpu_arm(args, spec: dict) -> None:
                        ["sequence_mean", "token_mean", "length_weighted"][spec["reduction"]],
                        "parallelism": f"token-sharded x{world}", "in_place": True, "kernel": plan,
                        "launch": "eager" if graph is None else "one CUDA graph per pass",
-                       "sharding": "contiguous row ranges of equal traffic" if world > 1 else "single range",
+                       "sharding": "contiguous row ranges of equal estimated kernel time" if world > 1 else "single range",
                        "exchange": ("reduce kernel over NVLink peer memory" if peer and world > 1 else
                                     "reduce kernel, own region only" if peer else
                                     "one NCCL all-reduce per pass" if world > 1 else "none"),

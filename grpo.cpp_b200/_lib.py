@@ -39,7 +39,9 @@ SIGNATURES = {
     "grpo_b200_loss_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _flt, _flt, _vp, _vp, _vp]),
     "grpo_b200_logits_workspace_bytes": (_sz, [_i64]),
     "grpo_b200_logits": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _flt, _flt,
-                                _int, _int, _vp, _vp, _vp, _sz, _vp]),
+                                _int, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "grpo_b200_row_order_bytes": (_sz, [_i64]),
+    "grpo_b200_row_order": (_int, [_vp, _i64, _vp, _vp]),
     "grpo_b200_exchange_bytes": (_sz, [_i64]),
     "grpo_b200_exchange_create": (_int, [_i64, C.POINTER(_vp)]),
     "grpo_b200_exchange_export": (_int, [_vp, C.c_char_p]),
@@ -47,8 +49,8 @@ SIGNATURES = {
     "grpo_b200_exchange_close": (_int, [_vp]),
     "grpo_b200_exchange_destroy": (_int, [_vp]),
     "grpo_b200_logits_sharded": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _flt,
-                                        _flt, _int, _int, _vp, _vp, _vp, _sz, C.POINTER(_vp), _int, _int, _i64, _vp,
-                                        _int, _flt, _vp, _vp, _vp, _vp]),
+                                        _flt, _int, _int, _vp, _vp, _vp, _vp, _sz, C.POINTER(_vp), _int, _int, _i64,
+                                        _vp, _int, _flt, _vp, _vp, _vp, _vp]),
     "grpo_b200_logits_set_variant": (_int, [_int]),
     "grpo_b200_logits_variant_name": (C.c_char_p, [_int]),
     "grpo_b200_logits_plan": (C.c_char_p, [_vp, _vp, _int, _int, _int]),

@@ -174,8 +174,9 @@ namespace {
 int logits_pass(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
                 const int32_t* selected, const float* advantages, const float* weights, const int32_t* mask,
                 int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P, float clip_eps, float beta,
-                int kernel, int check_inputs, float* selected_logp, grpo_b200_result_t* result, void* workspace,
-                size_t workspace_bytes, const ExchangeArgs& x, grpo_b200_stream_t stream) {
+                int kernel, int check_inputs, float* selected_logp, const int32_t* row_order,
+                grpo_b200_result_t* result, void* workspace, size_t workspace_bytes, const ExchangeArgs& x,
+                grpo_b200_stream_t stream) {
     if (!logits || !dlogits) return invalid("logits_and_dlogits must not be null");
     if (!logp_old || !logp_ref || !selected || !advantages || !weights || !mask || !result)
         return invalid("device pointers must not be null");
@@ -207,6 +208,7 @@ int logits_pass(const float* logits, float* dlogits, const float* logp_old, cons
     a.P = P;
     a.clip_eps = clip_eps;
     a.beta = beta;
+    a.row_order = row_order;
     a.rows = static_cast<RowRecord*>(workspace);
     a.selected_logp = selected_logp;
     a.result = result;
@@ -230,12 +232,24 @@ extern "C" {
 int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old, const float* logp_ref,
                      const int32_t* selected, const float* advantages, const float* weights, const int32_t* mask,
                      int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P, float clip_eps,
-                     float beta, int kernel, int check_inputs, float* selected_logp, grpo_b200_result_t* result,
-                     void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream) {
+                     float beta, int kernel, int check_inputs, float* selected_logp, const int32_t* row_order,
+                     grpo_b200_result_t* result, void* workspace, size_t workspace_bytes,
+                     grpo_b200_stream_t stream) {
     ExchangeArgs x = {};
     return logits_pass(logits, dlogits, logp_old, logp_ref, selected, advantages, weights, mask, n_rows, row_offset,
-                       tokens_per_seq, V, P, clip_eps, beta, kernel, check_inputs, selected_logp, result, workspace,
-                       workspace_bytes, x, stream);
+                       tokens_per_seq, V, P, clip_eps, beta, kernel, check_inputs, selected_logp, row_order, result,
+                       workspace, workspace_bytes, x, stream);
+}
+
+size_t grpo_b200_row_order_bytes(int64_t n_rows) {
+    return n_rows > 0 ? (static_cast<size_t>(n_rows) + 2) * sizeof(int32_t) : 0;
+}
+
+int grpo_b200_row_order(const int32_t* mask, int64_t n_rows, int32_t* order, grpo_b200_stream_t stream) {
+    if (!mask || !order) return invalid("device pointers must not be null");
+    if (n_rows <= 0 || n_rows > kIntMax) return invalid("n_rows must lie in [1, INT_MAX]");
+    GRPO_CUDA_TRY(launch_row_order(mask, n_rows, order, reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
 }
 
 size_t grpo_b200_exchange_bytes(int64_t n_seq) {
@@ -292,8 +306,8 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                              const int32_t* selected, const float* advantages, const float* weights,
                              const int32_t* mask, int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P,
                              float clip_eps, float beta, int kernel, int check_inputs, float* selected_logp,
-                             grpo_b200_result_t* result, void* workspace, size_t workspace_bytes,
-                             void* const* regions, int rank, int world, int64_t n_seq, const int32_t* next_mask,
+                             const int32_t* row_order, grpo_b200_result_t* result, void* workspace,
+                             size_t workspace_bytes, void* const* regions, int rank, int world, int64_t n_seq, const int32_t* next_mask,
                              int reduction, float length_alpha, float* next_weights, int32_t* next_meta,
                              double* next_lengths, grpo_b200_stream_t stream) {
     if (world < 1 || world > kExchangeMaxWorld) return invalid("world must lie in [1, 8]");
@@ -320,8 +334,8 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
     x.meta_out = next_meta;
     x.lengths_out = next_lengths;
     return logits_pass(logits, dlogits, logp_old, logp_ref, selected, advantages, weights, mask, n_rows, row_offset,
-                       tokens_per_seq, V, P, clip_eps, beta, kernel, check_inputs, selected_logp, result, workspace,
-                       workspace_bytes, x, stream);
+                       tokens_per_seq, V, P, clip_eps, beta, kernel, check_inputs, selected_logp, row_order, result,
+                       workspace, workspace_bytes, x, stream);
 }
 
 int grpo_b200_logits_set_variant(int variant) {

@@ -204,6 +204,7 @@ struct LogitsArgs {
     int tokens_per_seq;
     int V, P;
     float clip_eps, beta;
+    const int32_t* row_order;  // nullable: {n_active, n_masked, active rows ascending, masked rows ascending}
     RowRecord* rows;    // [n_rows] per-row hand-over between the row kernel and the reduce kernel
     float* selected_logp;
     grpo_b200_result_t* result;
@@ -257,6 +258,7 @@ cudaError_t launch_count_lengths_f64(const int32_t* mask, long long n_rows, long
                                      int tokens_per_seq, long long n_seq, double* lengths, cudaStream_t stream);
 cudaError_t launch_weights_f64(const double* lengths, long long n_seq, int reduction, float alpha,
                                float* weights, int32_t* meta, cudaStream_t stream);
+cudaError_t launch_row_order(const int32_t* mask, long long n_rows, int32_t* order, cudaStream_t stream);
 cudaError_t launch_group_advantages(const float* rewards, int B, int G, int mode, float eps,
                                     float* advantages, int32_t* meta, cudaStream_t stream);
 

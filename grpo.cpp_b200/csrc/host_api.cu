@@ -233,6 +233,7 @@ struct LogitsMeta {
     int32_t* mask_d;
     float* adv_d;
     float* w_d;
+    int32_t* order_d;  // {n_active, n_masked, active rows, masked rows}: balanced row order for the row kernel
     grpo_b200_result_t* result_d;
     void* work_d;
     size_t work_bytes;
@@ -240,12 +241,14 @@ struct LogitsMeta {
 };
 
 size_t logits_meta_bytes(const Shape& shape) {
-    return 4 * slice(shape.tokens * 4) + 2 * slice(shape.sequences * 4) + slice(sizeof(grpo_b200_result_t)) +
+    return 4 * slice(shape.tokens * 4) + 2 * slice(shape.sequences * 4) + slice((shape.tokens + 2) * 4) +
+           slice(sizeof(grpo_b200_result_t)) +
            slice(grpo_b200_logits_workspace_bytes(static_cast<int64_t>(shape.tokens)));
 }
 
-// Packs old/ref/selected/mask/advantages/weights into pinned memory in the device layout and
-// issues the single upload.
+// Packs old/ref/selected/mask/advantages/weights and the row order (the mask is on the host here,
+// so the partition into active and masked rows costs one pass over it) into pinned memory in the
+// device layout and issues the single upload.
 cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, const float* lp_old,
                               const float* lp_ref, const int32_t* selected, const float* adv,
                               const float* weights, const int32_t* mask, LogitsMeta& m) {
@@ -257,6 +260,7 @@ cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, cons
     m.mask_d = bump.take<int32_t>(n);
     m.adv_d = bump.take<float>(s);
     m.w_d = bump.take<float>(s);
+    m.order_d = bump.take<int32_t>(n + 2);
     const size_t packed = static_cast<size_t>(bump.base + bump.off - dev_start);
     m.result_d = bump.take<grpo_b200_result_t>(1);
     m.work_bytes = grpo_b200_logits_workspace_bytes(static_cast<int64_t>(n));
@@ -272,6 +276,16 @@ cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, cons
     put(mask, n * 4, m.mask_d);
     put(adv, s * 4, m.adv_d);
     put(weights, s * 4, m.w_d);
+    {
+        int32_t* order_h = reinterpret_cast<int32_t*>(h + (reinterpret_cast<char*>(m.order_d) - dev_start));
+        size_t n_active = 0;
+        for (size_t i = 0; i < n; i++) n_active += mask[i] != 0;
+        order_h[0] = static_cast<int32_t>(n_active);
+        order_h[1] = static_cast<int32_t>(n - n_active);
+        int32_t* active = order_h + 2;
+        int32_t* masked = active + n_active;
+        for (size_t i = 0; i < n; i++) *(mask[i] != 0 ? active : masked)++ = static_cast<int32_t>(i);
+    }
     m.result_h = reinterpret_cast<grpo_b200_result_t*>(arena.pinned + slice(packed));
     return cudaMemcpyAsync(dev_start, h, packed, cudaMemcpyHostToDevice, nullptr);
 }
@@ -377,7 +391,7 @@ int grpo_b200_logits_device_inplace_host(float* logits_and_dlogits, const float*
                                     mask, m));
     if (int rc = grpo_b200_logits(logits_and_dlogits, logits_and_dlogits, m.old_d, m.ref_d, m.sel_d, m.adv_d,
                                   m.w_d, m.mask_d, static_cast<int64_t>(shape.tokens), 0, T, V, P, clip_eps, beta,
-                                  kernel, 0, nullptr, m.result_d, m.work_d, m.work_bytes, nullptr))
+                                  kernel, 0, nullptr, m.order_d, m.result_d, m.work_d, m.work_bytes, nullptr))
         return rc;
     GRPO_CUDA_TRY(cudaMemcpyAsync(m.result_h, m.result_d, sizeof(*m.result_h), cudaMemcpyDeviceToHost, nullptr));
     GRPO_CUDA_TRY(cudaStreamSynchronize(nullptr));
@@ -433,7 +447,7 @@ int grpo_b200_logits_host(const float* logits, size_t n_logits, const float* log
     GRPO_CUDA_TRY(cudaMemcpyAsync(logits_d, logits, total * 4, cudaMemcpyHostToDevice, nullptr));
     if (int rc = grpo_b200_logits(logits_d, logits_d, m.old_d, m.ref_d, m.sel_d, m.adv_d, m.w_d, m.mask_d,
                                   static_cast<int64_t>(shape.tokens), 0, T, V, V, clip_eps, beta, kernel, 1,
-                                  nullptr, m.result_d, m.work_d, m.work_bytes, nullptr))
+                                  nullptr, m.order_d, m.result_d, m.work_d, m.work_bytes, nullptr))
         return rc;
     GRPO_CUDA_TRY(cudaMemcpyAsync(m.result_h, m.result_d, sizeof(*m.result_h), cudaMemcpyDeviceToHost, nullptr));
     GRPO_CUDA_TRY(cudaMemcpyAsync(dlogits_out, logits_d, total * 4, cudaMemcpyDeviceToHost, nullptr));
@@ -562,7 +576,7 @@ int grpo_b200_benchmark_logits_host(const float* logits, size_t n_logits, const 
     auto pass = [&](int kernel) {
         return grpo_b200_logits(in_d, out_d, m.old_d, m.ref_d, m.sel_d, m.adv_d, m.w_d, m.mask_d,
                                 static_cast<int64_t>(shape.tokens), 0, T, V, V, clip_eps, beta, kernel, 0, nullptr,
-                                m.result_d, m.work_d, m.work_bytes, nullptr);
+                                m.order_d, m.result_d, m.work_d, m.work_bytes, nullptr);
     };
     auto time_once = [&](int kernel, float& ms_per_pass) -> int {
         GRPO_CUDA_TRY(cudaEventRecord(arena.ev[0], nullptr));

@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE_CHUNKS = TJ * THREADS;
     constexpr int TILES = VEC / TJ;
-    constexpr int BATCH = 256;  // rows whose scalars are staged at once
+    constexpr int BATCH = 128;  // rows whose scalars are staged at once
     static_assert(VEC % TJ == 0, "tiles must cover the per-thread chunks exactly");
     static_assert(WARPS <= 32, "warp indices fit one lane each");
 
@@ -336,12 +336,16 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     __shared__ float meta_adv[BATCH];
     __shared__ float meta_w[BATCH];
     __shared__ unsigned char meta_mask[BATCH];
+    __shared__ int meta_row[BATCH];
     __shared__ unsigned q_cons_final;
     __shared__ int abort_sh;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const bool is_producer = warp == WARPS;
+    // The reduce kernel that follows in the stream may be made resident as this grid's CTAs retire
+    // and run its prologue; it still waits for this whole grid before it reads anything written here.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // The pass's control words start from zero without a separate clearing launch: block 0 is
     // resident from the first instant (the grid never exceeds what fits at once), a wait gives up
     // only after seconds, and the reduce kernel that reads them runs after this kernel.
@@ -387,8 +391,21 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     __syncthreads();
     if (CLUSTER > 1) cg::this_cluster().sync();  // peers' barriers exist before anyone arrives on them remotely
 
-    // Rows of this cluster: cluster_id + k * n_clusters, k = 0 .. n_mine-1, walked in batches.
-    const int n_mine = cluster_id < n_rows ? (n_rows - cluster_id + n_clusters - 1) / n_clusters : 0;
+    // Rows of this cluster.  Without a row order: cluster_id + k * n_clusters, k = 0 .. n_mine-1,
+    // whatever their masks.  With one (row_order = {n_active, n_masked, active rows..., masked
+    // rows...}): every n_clusters-th ACTIVE row and every n_clusters-th MASKED row, so that all
+    // clusters carry the same load to within a row, interleaved evenly (slot k is an active row
+    // when floor((k+1) * mine_active / n_mine) steps up) so that zero fills keep overlapping with
+    // the active rows' phases.
+    const int* order = a.row_order;
+    const int total_active = order ? order[0] : 0;
+    const int total_masked = order ? order[1] : 0;
+    const int* active_rows = order ? order + 2 : nullptr;
+    const int* masked_rows = order ? order + 2 + total_active : nullptr;
+    const int mine_active = order && cluster_id < total_active ? (total_active - cluster_id + n_clusters - 1) / n_clusters : 0;
+    const int mine_masked = order && cluster_id < total_masked ? (total_masked - cluster_id + n_clusters - 1) / n_clusters : 0;
+    const int n_mine = order ? mine_active + mine_masked
+                             : (cluster_id < n_rows ? (n_rows - cluster_id + n_clusters - 1) / n_clusters : 0);
 
     unsigned q = 0;     // consumers: tiles consumed; producer: tiles requested
     bool alive = true;  // false after a wait timed out: skip the ring, keep meeting barriers
@@ -408,22 +425,29 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
         //      issued); lane 0 requests every tile of every active row, in order, as the ring's
         //      stages come free.  It shares nothing with the consumers but the ring.
         if (n_tiles > 0) {
-            auto group_mask = [&](int base) -> unsigned {
+            // lane l's candidate of the group starting at `base`: the row to load, or -1.  Without a
+            // row order the candidates are this cluster's rows in turn (masked ones give -1); with
+            // one they are its active rows in turn.
+            const int n_cand = order ? mine_active : n_mine;
+            auto group_rows = [&](int base) -> int {
                 const int k = base + lane;
-                int mk = 0;
-                if (k < n_mine) mk = a.mask[static_cast<size_t>(cluster_id) + static_cast<size_t>(k) * n_clusters] != 0;
-                return __ballot_sync(0xffffffffu, mk);
+                if (k >= n_cand) return -1;
+                const size_t at = static_cast<size_t>(cluster_id) + static_cast<size_t>(k) * n_clusters;
+                if (order) return active_rows[at];
+                return a.mask[at] != 0 ? static_cast<int>(at) : -1;
             };
-            unsigned next_bits = group_mask(0);
-            for (int base = 0; base < n_mine && alive; base += 32) {
-                unsigned bits = next_bits;
-                if (base + 32 < n_mine) next_bits = group_mask(base + 32);
-                if (lane == 0) {
-                    while (bits != 0 && alive) {
-                        const int k_row = base + __ffs(bits) - 1;
-                        bits &= bits - 1;
-                        const size_t p_row = static_cast<size_t>(cluster_id) + static_cast<size_t>(k_row) * n_clusters;
-                        const float* row_src = a.logits + p_row * static_cast<size_t>(a.P) + 4 * static_cast<size_t>(c0);
+            int next_row = group_rows(0);
+            for (int base = 0; base < n_cand && alive; base += 32) {
+                const int my_row = next_row;
+                if (base + 32 < n_cand) next_row = group_rows(base + 32);
+                unsigned bits = __ballot_sync(0xffffffffu, my_row >= 0);
+                while (bits != 0) {  // uniform: every lane walks the same bits
+                    const int src_lane = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    const int p_row = __shfl_sync(0xffffffffu, my_row, src_lane);
+                    if (lane == 0 && alive) {
+                        const float* row_src =
+                            a.logits + static_cast<size_t>(p_row) * static_cast<size_t>(a.P) + 4 * static_cast<size_t>(c0);
                         for (int t = 0; t < n_tiles; t++) {
                             const unsigned slot = q % STAGES;
                             const unsigned parity = (q / STAGES) & 1u;
@@ -450,8 +474,18 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
         const int batch_rows = min(BATCH, n_mine - batch_first);
         consumer_sync(THREADS);  // every consumer is done with the previous batch's scalars
         for (int i = tid; i < batch_rows; i += THREADS) {
-            const size_t r = static_cast<size_t>(cluster_id) + static_cast<size_t>(batch_first + i) * n_clusters;
-            const int mk = a.mask[r];
+            const long long k = batch_first + i;
+            size_t r = static_cast<size_t>(cluster_id) + static_cast<size_t>(k) * n_clusters;
+            int mk;
+            if (order) {
+                const long long before = k * mine_active / n_mine;  // active rows among this cluster's first k
+                mk = (k + 1) * mine_active / n_mine > before;
+                const size_t nth = mk ? static_cast<size_t>(before) : static_cast<size_t>(k - before);
+                r = static_cast<size_t>((mk ? active_rows : masked_rows)[static_cast<size_t>(cluster_id) + nth * n_clusters]);
+            } else {
+                mk = a.mask[r];
+            }
+            meta_row[i] = static_cast<int>(r);
             meta_mask[i] = mk != 0;
             if (mk != 0) {
                 const long long seq = (a.row_offset + static_cast<long long>(r)) / a.tokens_per_seq;
@@ -466,7 +500,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
 
         // ---- consumer warps
         for (int k_row = 0; k_row < batch_rows; k_row++) {
-            const size_t row = static_cast<size_t>(cluster_id) + static_cast<size_t>(batch_first + k_row) * n_clusters;
+            const size_t row = static_cast<size_t>(meta_row[k_row]);
             GRPO_TL(0);  // row start
             float4* out = reinterpret_cast<float4*>(a.dlogits + row * static_cast<size_t>(a.P)) + c0;
 
@@ -897,12 +931,19 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
             if (hist[i] != 0) atomicAdd(counts + first_seq + i, hist[i]);
     }
 
+    // Everything above and the loads just below depend on nothing the row kernel writes: they may run
+    // while its last CTAs are still working (programmatic dependent launch).  From here on its
+    // records, status word and cleared ticket counter are needed.
+    const bool row_active = row < a.n_rows && a.mask[row] != 0;
+    RowScalars sc = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (row_active) sc = load_row_scalars(a, row);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     double v[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
     if (row < a.n_rows) {
         float lp_new = 0.0f;
-        if (a.mask[row] != 0) {
+        if (row_active) {
             const RowRecord r = a.rows[row];
-            const RowScalars sc = load_row_scalars(a, row);
             const double lse = static_cast<double>(r.m) + log(r.z);
             lp_new = static_cast<float>(static_cast<double>(r.x_sel) - lse);
             const TokenTerms t = token_terms<true>(lp_new, sc.lp_old, sc.lp_ref, sc.adv, sc.w, a.clip_eps, a.beta);
@@ -1171,9 +1212,18 @@ cudaError_t launch_logits_streaming(bool check, const LogitsArgs& a, cudaStream_
 }
 
 cudaError_t launch_logits_reduce(const LogitsArgs& a, const ExchangeArgs& x, cudaStream_t stream) {
-    const unsigned blocks = static_cast<unsigned>((a.n_rows + kReduceThreads - 1) / kReduceThreads);
-    logits_reduce_kernel<<<blocks, kReduceThreads, 0, stream>>>(a, x);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((a.n_rows + kReduceThreads - 1) / kReduceThreads), 1, 1);
+    cfg.blockDim = dim3(kReduceThreads, 1, 1);
+    cfg.stream = stream;
+    // programmatic dependent launch: the blocks may start before the row kernel has drained; the
+    // kernel itself waits (griddepcontrol.wait) before touching what the row kernel produced
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, logits_reduce_kernel, a, x);
 }
 
 }  // namespace grpo_b200

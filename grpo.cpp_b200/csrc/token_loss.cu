@@ -178,6 +178,53 @@ __global__ void __launch_bounds__(1024) weights_kernel(const LEN* __restrict__ l
     block_weights<1024>(lengths, n_seq, reduction, alpha, weights, meta, scratch);
 }
 
+// Stable partition of the row indices by mask: order = {n_active, n_masked, active rows ascending,
+// masked rows ascending}.  One block; every thread owns a contiguous run of rows, counts its active
+// ones, takes its offsets from a block-wide exclusive scan, and writes its rows out.
+__global__ void __launch_bounds__(1024) row_order_kernel(const int32_t* __restrict__ mask, long long n_rows,
+                                                         int32_t* __restrict__ order) {
+    __shared__ int warp_base[32];
+    __shared__ int total_sh;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long per = (n_rows + 1023) / 1024;
+    const long long lo = min(static_cast<long long>(tid) * per, n_rows), hi = min(lo + per, n_rows);
+    int count = 0;
+    for (long long i = lo; i < hi; i++) count += mask[i] != 0;
+    int incl = count;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_base[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int t = warp_base[lane];
+        int ti = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, ti, o);
+            if (lane >= o) ti += up;
+        }
+        warp_base[lane] = ti - t;
+        if (lane == 31) total_sh = ti;
+    }
+    __syncthreads();
+    const int total = total_sh;
+    long long a_pos = incl - count + warp_base[warp];
+    long long m_pos = lo - a_pos;
+    for (long long i = lo; i < hi; i++) {
+        if (mask[i] != 0)
+            order[2 + a_pos++] = static_cast<int32_t>(i);
+        else
+            order[2 + total + m_pos++] = static_cast<int32_t>(i);
+    }
+    if (tid == 0) {
+        order[0] = total;
+        order[1] = static_cast<int32_t>(n_rows - total);
+    }
+}
+
 // One thread per prompt walks its G rewards in order: Welford mean / M2 in double with
 // unfused IEEE operations, exactly the CPU sequence (src/cpu/grpo_loss.cpp:31-52).
 __global__ void __launch_bounds__(256) group_advantages_kernel(const float* __restrict__ rewards, int B, int G,
@@ -278,6 +325,11 @@ cudaError_t launch_count_lengths_f64(const int32_t* mask, long long n_rows, long
 cudaError_t launch_weights_f64(const double* lengths, long long n_seq, int reduction, float alpha, float* weights,
                                int32_t* meta, cudaStream_t stream) {
     weights_kernel<double><<<1, 1024, 0, stream>>>(lengths, n_seq, reduction, alpha, weights, meta);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_row_order(const int32_t* mask, long long n_rows, int32_t* order, cudaStream_t stream) {
+    row_order_kernel<<<1, 1024, 0, stream>>>(mask, n_rows, order);
     return cudaGetLastError();
 }
 

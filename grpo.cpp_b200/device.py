@@ -140,9 +140,10 @@ def logits(logits_t: torch.Tensor, logp_old, logp_ref, selected, advantages, wei
            tokens_per_seq: int, V: int, clip_eps: float, beta: float, *, dlogits: torch.Tensor | None = None,
            row_offset: int = 0, kernel: int = CudaLogitsKernel.fused, check_inputs: bool = False,
            selected_logp: torch.Tensor | None = None, result: torch.Tensor | None = None,
-           workspace: torch.Tensor | None = None) -> torch.Tensor:
+           workspace: torch.Tensor | None = None, row_order: torch.Tensor | None = None) -> torch.Tensor:
     """Logits path on device tensors: ``logits_t`` is ``[n_rows, P]`` fp32; ``dlogits=None`` means in
-    place.  Returns the result record."""
+    place.  ``row_order`` (from :func:`row_order` on the same mask) balances the rows over the
+    clusters.  Returns the result record."""
     if logits_t.dim() != 2:
         raise ValueError("logits must be [n_rows, P]")
     n_rows, P = logits_t.shape
@@ -160,8 +161,27 @@ def logits(logits_t: torch.Tensor, logp_old, logp_ref, selected, advantages, wei
         _check_tensor(weights, torch.float32, "weights"), _check_tensor(mask, torch.int32, "mask"),
         n_rows, row_offset, tokens_per_seq, V, P, float(clip_eps), float(beta), int(kernel), int(check_inputs),
         None if selected_logp is None else _check_tensor(selected_logp, torch.float32, "selected_logp"),
+        _order_ptr(row_order, n_rows),
         _check_tensor(result, torch.float64, "result"), workspace.data_ptr(), workspace.numel(), _stream()))
     return result
+
+
+def _order_ptr(row_order, n_rows: int):
+    if row_order is None:
+        return None
+    if row_order.numel() != n_rows + 2:
+        raise ValueError("row_order must come from row_order() on a mask over the same rows")
+    return _check_tensor(row_order, torch.int32, "row_order")
+
+
+def row_order(mask: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``[n_active, n_masked, active rows..., masked rows...]`` (int32, ``len(mask) + 2``): the stable
+    partition of the local row indices by ``mask`` that :func:`logits` takes as ``row_order``."""
+    m = _check_tensor(mask, torch.int32, "mask")
+    if out is None:
+        out = torch.empty(mask.numel() + 2, dtype=torch.int32, device=mask.device)
+    _lib.check(_lib.lib().grpo_b200_row_order(m, mask.numel(), _check_tensor(out, torch.int32, "row_order"), _stream()))
+    return out
 
 
 class PeerExchange:
@@ -215,7 +235,7 @@ def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advanta
                    next_meta: torch.Tensor, result: torch.Tensor, workspace: torch.Tensor,
                    next_lengths: torch.Tensor | None = None, row_offset: int = 0,
                    kernel: int = CudaLogitsKernel.fused, check_inputs: bool = False,
-                   selected_logp: torch.Tensor | None = None) -> torch.Tensor:
+                   selected_logp: torch.Tensor | None = None, row_order: torch.Tensor | None = None) -> torch.Tensor:
     """:func:`logits` in place on this rank's rows; the pass's last kernel also counts ``next_mask``'s
     valid tokens, sums the result record and the counts over the ranks through their exchange
     regions, and writes the next pass's weights (``next_weights`` may be ``weights``) and
@@ -233,6 +253,7 @@ def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advanta
         _check_tensor(weights, torch.float32, "weights"), _check_tensor(mask, torch.int32, "mask"),
         n_rows, row_offset, tokens_per_seq, V, P, float(clip_eps), float(beta), int(kernel), int(check_inputs),
         None if selected_logp is None else _check_tensor(selected_logp, torch.float32, "selected_logp"),
+        _order_ptr(row_order, n_rows),
         _check_tensor(result, torch.float64, "result"), workspace.data_ptr(), workspace.numel(),
         exchange.regions, exchange.rank, exchange.world, exchange.n_seq,
         _check_tensor(next_mask, torch.int32, "next_mask"), int(reduction), float(length_alpha),

@@ -14,7 +14,8 @@ the host (apps/03_two_gpu_train.cu:200-215,247-281); token sharding with ``token
 ``length_weighted`` needs the global lengths, which is what exchange 1 provides.
 
 ``prepare`` depends only on the mask, so it runs once per rollout batch; ``step`` runs once per
-optimisation pass over that batch.
+optimisation pass over that batch.  ``prepare`` also partitions the local rows into active and
+masked ones, which lets the row kernel deal its clusters equal loads.
 """
 from __future__ import annotations
 
@@ -32,21 +33,24 @@ def shard_rows(n_rows: int, world: int, rank: int) -> tuple[int, int]:
     return rank * base + min(rank, rem), base + (1 if rank < rem else 0)
 
 
-def shard_rows_balanced(mask, world: int, V: int, P: int) -> list[tuple[int, int]]:
-    """Contiguous row ranges ``[(row_offset, row_count), ...]`` of nearly equal HBM traffic.
+def shard_rows_balanced(mask, world: int, V: int, P: int, masked_cost: float = 0.8) -> list[tuple[int, int]]:
+    """Contiguous row ranges ``[(row_offset, row_count), ...]`` of nearly equal kernel time.
 
-    An active row costs ``V + P`` floats (one read, one write), a masked row ``P`` (zeros written,
+    An active row moves ``V + P`` floats (one read, one write), a masked row ``P`` (zeros written,
     nothing read), so with ragged masks equal row counts are not equal work: the rank that happens
     to hold the longest responses finishes last and everyone waits for it in the result exchange.
+    A masked row's plain zero-fill also runs nearer to the memory rate than an active row's
+    read-compute-write, so it is charged ``masked_cost * P`` (0.8 fits the row kernel's measured
+    times on the GPT-2-shaped batch: a masked row costs about 0.4 of an active one).
     ``mask`` is the whole batch's host mask; every rank computes the same cut points from it."""
     import numpy as np
     m = np.asarray(mask).reshape(-1) != 0
-    cost = np.where(m, V + P, P).astype(np.int64)
-    prefix = np.concatenate(([0], np.cumsum(cost)))
-    total = int(prefix[-1])
+    cost = np.where(m, float(V + P), masked_cost * P)
+    prefix = np.concatenate(([0.0], np.cumsum(cost)))
+    total = float(prefix[-1])
     cuts = [0]
     for r in range(1, world):
-        target = total * r // world
+        target = total * r / world
         cut = int(np.searchsorted(prefix, target, side="left"))
         cuts.append(min(max(cut, cuts[-1]), m.size))
     cuts.append(m.size)
@@ -86,6 +90,7 @@ class ShardedBoundary:
         self.lengths_f64 = self.xchg[5:]
         self.workspace = ops.logits_workspace(self.n_local, device)
         self.exchange = None  # set by enable_peer_exchange
+        self.row_order = None  # set by prepare: the upcoming pass's balanced row order
 
     def _all_reduce(self, t: torch.Tensor) -> None:
         if self.world > 1:
@@ -98,13 +103,14 @@ class ShardedBoundary:
         self.ops.count_lengths(mask_local, self.S, self.T, self.row_offset, self.lengths)
         self._all_reduce(self.lengths)
         self.ops.weights_from_lengths(self.lengths, self.reduction, self.alpha, self.weights, self.meta)
+        self.row_order = self.ops.row_order(mask_local, self.row_order)
 
     def step(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,
              kernel: int = CudaLogitsKernel.fused) -> torch.Tensor:
         """Kernel on the local rows (in place), then exchange 2.  Returns the global result record."""
         self.ops.logits(logits_local, logp_old, logp_ref, selected, advantages, self.weights, mask_local,
                         self.T, self.V, self.clip_eps, self.beta, row_offset=self.row_offset, kernel=kernel,
-                        result=self.result, workspace=self.workspace)
+                        result=self.result, workspace=self.workspace, row_order=self.row_order)
         self._all_reduce(self.result)
         return self.result
 
@@ -121,9 +127,11 @@ class ShardedBoundary:
         self.ops.count_lengths_f64(nxt, self.S, self.T, self.row_offset, self.lengths_f64)
         self.ops.logits(logits_local, logp_old, logp_ref, selected, advantages, self.weights, mask_local,
                         self.T, self.V, self.clip_eps, self.beta, row_offset=self.row_offset, kernel=kernel,
-                        result=self.result, workspace=self.workspace)
+                        result=self.result, workspace=self.workspace, row_order=self.row_order)
         self._all_reduce(self.xchg)
         self.ops.weights_from_lengths_f64(self.lengths_f64, self.reduction, self.alpha, self.weights, self.meta)
+        if next_mask_local is not None:
+            self.row_order = self.ops.row_order(next_mask_local, self.row_order)
         return self.result
 
     def enable_peer_exchange(self) -> None:
@@ -154,7 +162,10 @@ class ShardedBoundary:
                                 self.T, self.V, self.clip_eps, self.beta, exchange=self.exchange, next_mask=nxt,
                                 reduction=self.reduction, length_alpha=self.alpha, next_weights=self.weights,
                                 next_meta=self.meta, next_lengths=self.lengths_f64, result=self.result,
-                                workspace=self.workspace, row_offset=self.row_offset, kernel=kernel)
+                                workspace=self.workspace, row_offset=self.row_offset, kernel=kernel,
+                                row_order=self.row_order)
+        if next_mask_local is not None:
+            self.row_order = self.ops.row_order(next_mask_local, self.row_order)
         return self.result
 
     def capture(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,

@@ -180,14 +180,26 @@ int grpo_b200_loss_noalloc(const float* logp_new, const float* logp_old, const f
  * buffer of the same row stride P.  Rows are the local rows [row_offset, row_offset + n_rows).
  * kernel: GRPO_B200_LOGITS_FUSED or _SEPARATE.  check_inputs != 0 additionally records rows
  * with a non-finite logit or an out-of-range selected id in result->bad_inputs.
- * selected_logp (nullable) receives log p(selected) per row (0 for masked rows). */
+ * selected_logp (nullable) receives log p(selected) per row (0 for masked rows).
+ * row_order (nullable) is the output of grpo_b200_row_order for this mask: with it the row
+ * kernel deals every cluster the same number of active and of masked rows, evenly interleaved,
+ * instead of every n-th row whatever its mask; results do not depend on it. */
 size_t grpo_b200_logits_workspace_bytes(int64_t n_rows);
 int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
                      const float* logp_ref, const int32_t* selected, const float* advantages,
                      const float* weights, const int32_t* mask, int64_t n_rows, int64_t row_offset,
                      int tokens_per_seq, int V, int P, float clip_eps, float beta, int kernel,
-                     int check_inputs, float* selected_logp, grpo_b200_result_t* result,
-                     void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream);
+                     int check_inputs, float* selected_logp, const int32_t* row_order,
+                     grpo_b200_result_t* result, void* workspace, size_t workspace_bytes,
+                     grpo_b200_stream_t stream);
+
+/* Stable partition of the local row indices by mask, for the row_order argument above:
+ * order[n_rows + 2] = {n_active, n_masked, active rows ascending, masked rows ascending}.
+ * No counterpart in the reference (its kernels take one row per block, in index order,
+ * src/cuda/grpo_loss_cuda.cu:551-582).  Depends on the mask only: computed once per batch. */
+size_t grpo_b200_row_order_bytes(int64_t n_rows);
+int grpo_b200_row_order(const int32_t* mask, int64_t n_rows, int32_t* order,
+                        grpo_b200_stream_t stream);
 
 /* Token-sharded logits path with the pass's exchange done by the library's own kernel over
  * NVLink peer memory.  No counterpart in the reference, whose two-GPU demo shards whole
@@ -221,8 +233,9 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                              const float* advantages, const float* weights, const int32_t* mask,
                              int64_t n_rows, int64_t row_offset, int tokens_per_seq, int V, int P,
                              float clip_eps, float beta, int kernel, int check_inputs,
-                             float* selected_logp, grpo_b200_result_t* result, void* workspace,
-                             size_t workspace_bytes, void* const* regions, int rank, int world,
+                             float* selected_logp, const int32_t* row_order,
+                             grpo_b200_result_t* result, void* workspace, size_t workspace_bytes,
+                             void* const* regions, int rank, int world,
                              int64_t n_seq, const int32_t* next_mask, int reduction,
                              float length_alpha, float* next_weights, int32_t* next_meta,
                              double* next_lengths, grpo_b200_stream_t stream);

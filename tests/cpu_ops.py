@@ -46,6 +46,13 @@ def weights_from_lengths(lengths, reduction, length_alpha=0.0, out=None, meta=No
     return out, meta
 
 
+def row_order(mask, out=None):
+    m = mask.numpy() != 0
+    idx = np.arange(m.size, dtype=np.int32)
+    order = np.concatenate(([int(m.sum()), int((~m).sum())], idx[m], idx[~m])).astype(np.int32)
+    return torch.from_numpy(order)
+
+
 def count_lengths_f64(mask, n_seq, tokens_per_seq, row_offset, out):
     out.copy_(count_lengths(mask, n_seq, tokens_per_seq, row_offset).to(torch.float64))
     return out

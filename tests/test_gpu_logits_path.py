@@ -362,3 +362,39 @@ def test_peer_exchange_pass_single_rank():
             assert sb.lengths_f64.cpu().numpy().astype(np.int64).tolist() == b.mask.reshape(b.S, b.T).sum(1).tolist()
     finally:
         sb.exchange.close()
+
+
+def test_row_order_partition_and_invariance():
+    """grpo_b200_row_order is the stable partition of the row indices by mask (bit-exact against
+    numpy), and a pass that uses it writes the same bits as one that does not, for cluster sizes
+    1 to 8 and masks from nearly empty to full."""
+    import torch
+    from grpo_cpp_b200 import device as D
+    rng = np.random.default_rng(8)
+    for n in (1, 31, 1024, 70001):
+        m = (rng.random(n) < 0.6).astype(np.int32)
+        got = D.row_order(torch.from_numpy(m).cuda()).cpu().numpy()
+        idx = np.arange(n, dtype=np.int32)
+        want = np.concatenate(([m.sum(), n - m.sum()], idx[m != 0], idx[m == 0])).astype(np.int32)
+        assert (got == want).all()
+    names = D.variants()
+    try:
+        for name, V, min_len in (("1x128x16", 1000, 1), ("4x128x16", 30000, 3), ("8x128x16", 50257, 1), ("2x512x16", 40000, 12)):
+            P = (V + 3) // 4 * 4 + 8
+            b = W.logits_case(3, 4, 12, V, sigma=2.0, min_len=min_len, reduction=W.TOKEN_MEAN, seed=len(name) + V)
+            t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+            old, ref, sel, adv, mask = t(b.logp_old), t(b.logp_ref), t(b.selected), t(b.advantages), t(b.mask)
+            lengths = D.count_lengths(mask, b.S, b.T)
+            weights, _ = D.weights_from_lengths(lengths, b.reduction, 0.0)
+            D.set_variant(names.index(name))
+            outs = []
+            for order in (None, D.row_order(mask)):
+                x = t(b.padded(P))
+                assert D.plan(x, V) == name
+                res = D.logits(x, old, ref, sel, adv, weights, mask, b.T, V, b.clip_eps, b.beta, row_order=order)
+                outs.append((x.cpu().numpy(), res.cpu().numpy()))
+            assert (outs[0][0] == outs[1][0]).all() and (outs[0][1] == outs[1][1]).all()
+            want = run_oracle(b)
+            assert_grad(outs[1][0][:, :V], want[2], name)
+    finally:
+        D.set_variant(-1)

@@ -138,11 +138,13 @@ def test_balanced_shards_cover_and_balance():
     rng = np.random.RandomState(0)
     T, S, V, P = 64, 96, 1000, 1024
     mask = W.prefix_mask(rng.randint(8, T + 1, S), T)
-    cost = np.where(mask != 0, V + P, P)
-    for world in (1, 2, 3, 8):
-        spans = shard_rows_balanced(mask, world, V, P)
-        assert spans[0][0] == 0 and sum(c for _, c in spans) == mask.size
-        for (o0, c0), (o1, _) in zip(spans, spans[1:]):
-            assert o0 + c0 == o1
-        work = [int(cost[o:o + c].sum()) for o, c in spans]
-        assert max(work) - min(work) <= 2 * (V + P)  # within a row or two of each other
+    for masked_cost in (1.0, 0.8):  # pure traffic; the default calibrated to the row kernel's times
+        cost = np.where(mask != 0, float(V + P), masked_cost * P)
+        for world in (1, 2, 3, 8):
+            spans = shard_rows_balanced(mask, world, V, P, masked_cost)
+            assert spans[0][0] == 0 and sum(c for _, c in spans) == mask.size
+            for (o0, c0), (o1, _) in zip(spans, spans[1:]):
+                assert o0 + c0 == o1
+            work = [cost[o:o + c].sum() for o, c in spans]
+            assert max(work) - min(work) <= 2 * (V + P)  # within a row or two of each other
+    assert shard_rows_balanced(mask, 8, V, P) == shard_rows_balanced(mask, 8, V, P, 0.8)
