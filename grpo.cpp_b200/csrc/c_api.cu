@@ -242,7 +242,9 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
 }
 
 size_t grpo_b200_row_order_bytes(int64_t n_rows) {
-    return n_rows > 0 ? (static_cast<size_t>(n_rows) + 2) * sizeof(int32_t) : 0;
+    // the order itself, then one scratch count per tile of 1024 rows
+    return n_rows > 0 ? (static_cast<size_t>(n_rows) + 2 + (static_cast<size_t>(n_rows) + 1023) / 1024) * sizeof(int32_t)
+                      : 0;
 }
 
 int grpo_b200_row_order(const int32_t* mask, int64_t n_rows, int32_t* order, grpo_b200_stream_t stream) {

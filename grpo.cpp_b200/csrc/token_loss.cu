@@ -179,49 +179,79 @@ __global__ void __launch_bounds__(1024) weights_kernel(const LEN* __restrict__ l
 }
 
 // Stable partition of the row indices by mask: order = {n_active, n_masked, active rows ascending,
-// masked rows ascending}.  One block; every thread owns a contiguous run of rows, counts its active
-// ones, takes its offsets from a block-wide exclusive scan, and writes its rows out.
-__global__ void __launch_bounds__(1024) row_order_kernel(const int32_t* __restrict__ mask, long long n_rows,
-                                                         int32_t* __restrict__ order) {
-    __shared__ int warp_base[32];
-    __shared__ int total_sh;
+// masked rows ascending}, in two launches over tiles of 1024 rows.  The first counts each tile's
+// active rows into a scratch tail of `order`; the second gives every tile its offsets (sum of the
+// counts before it) and scatters its rows, warp ballots providing the positions inside the tile.
+constexpr int kOrderTile = 1024;
+
+__global__ void __launch_bounds__(kOrderTile) row_order_count_kernel(const int32_t* __restrict__ mask,
+                                                                     long long n_rows, int32_t* __restrict__ counts) {
+    __shared__ int warp_count[kOrderTile / 32];
+    const long long i = static_cast<long long>(blockIdx.x) * kOrderTile + threadIdx.x;
+    const bool active = i < n_rows && mask[i] != 0;
+    const unsigned bits = __ballot_sync(0xffffffffu, active);
+    if ((threadIdx.x & 31) == 0) warp_count[threadIdx.x >> 5] = __popc(bits);
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        int c = warp_count[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
+        if (threadIdx.x == 0) counts[blockIdx.x] = c;
+    }
+}
+
+__global__ void __launch_bounds__(kOrderTile) row_order_scatter_kernel(const int32_t* __restrict__ mask,
+                                                                       long long n_rows,
+                                                                       const int32_t* __restrict__ counts,
+                                                                       int32_t* __restrict__ order) {
+    __shared__ int warp_count[kOrderTile / 32];
+    __shared__ long long sums[2];  // active rows before this tile; active rows in all
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const long long per = (n_rows + 1023) / 1024;
-    const long long lo = min(static_cast<long long>(tid) * per, n_rows), hi = min(lo + per, n_rows);
-    int count = 0;
-    for (long long i = lo; i < hi; i++) count += mask[i] != 0;
-    int incl = count;
+    // every block adds up the tile counts (a few hundred at most for the batches this serves)
+    long long before = 0, all = 0;
+    for (unsigned b = tid; b < gridDim.x; b += kOrderTile) {
+        const int c = counts[b];
+        all += c;
+        if (b < blockIdx.x) before += c;
+    }
+    __shared__ long long red[2][kOrderTile / 32];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
+    for (int o = 16; o > 0; o >>= 1) {
+        before += __shfl_down_sync(0xffffffffu, before, o);
+        all += __shfl_down_sync(0xffffffffu, all, o);
     }
-    if (lane == 31) warp_base[warp] = incl;
+    if (lane == 0) {
+        red[0][warp] = before;
+        red[1][warp] = all;
+    }
+    const long long i = static_cast<long long>(blockIdx.x) * kOrderTile + tid;
+    const bool in_range = i < n_rows;
+    const bool active = in_range && mask[i] != 0;
+    const unsigned bits = __ballot_sync(0xffffffffu, active);
+    if (lane == 0) warp_count[warp] = __popc(bits);
     __syncthreads();
-    if (warp == 0) {
-        const int t = warp_base[lane];
-        int ti = t;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int up = __shfl_up_sync(0xffffffffu, ti, o);
-            if (lane >= o) ti += up;
-        }
-        warp_base[lane] = ti - t;
-        if (lane == 31) total_sh = ti;
-    }
-    __syncthreads();
-    const int total = total_sh;
-    long long a_pos = incl - count + warp_base[warp];
-    long long m_pos = lo - a_pos;
-    for (long long i = lo; i < hi; i++) {
-        if (mask[i] != 0)
-            order[2 + a_pos++] = static_cast<int32_t>(i);
-        else
-            order[2 + total + m_pos++] = static_cast<int32_t>(i);
-    }
     if (tid == 0) {
-        order[0] = total;
-        order[1] = static_cast<int32_t>(n_rows - total);
+        long long s0 = 0, s1 = 0;
+        for (int w = 0; w < kOrderTile / 32; w++) {
+            s0 += red[0][w];
+            s1 += red[1][w];
+        }
+        sums[0] = s0;
+        sums[1] = s1;
+    }
+    int in_tile = __popc(bits & ((1u << lane) - 1u));  // active rows before this one: in its warp ...
+    for (int w = 0; w < warp; w++) in_tile += warp_count[w];  // ... and in the tile's earlier warps
+    __syncthreads();
+    const long long active_before = sums[0] + in_tile;
+    if (in_range) {
+        if (active)
+            order[2 + active_before] = static_cast<int32_t>(i);
+        else
+            order[2 + sums[1] + (i - active_before)] = static_cast<int32_t>(i);
+    }
+    if (blockIdx.x == 0 && tid == 0) {
+        order[0] = static_cast<int32_t>(sums[1]);
+        order[1] = static_cast<int32_t>(n_rows - sums[1]);
     }
 }
 
@@ -329,7 +359,12 @@ cudaError_t launch_weights_f64(const double* lengths, long long n_seq, int reduc
 }
 
 cudaError_t launch_row_order(const int32_t* mask, long long n_rows, int32_t* order, cudaStream_t stream) {
-    row_order_kernel<<<1, 1024, 0, stream>>>(mask, n_rows, order);
+    const unsigned tiles = static_cast<unsigned>((n_rows + kOrderTile - 1) / kOrderTile);
+    int32_t* counts = order + 2 + n_rows;  // scratch tail of the order buffer
+    row_order_count_kernel<<<tiles, kOrderTile, 0, stream>>>(mask, n_rows, counts);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    row_order_scatter_kernel<<<tiles, kOrderTile, 0, stream>>>(mask, n_rows, counts, order);
     return cudaGetLastError();
 }
 

@@ -169,17 +169,19 @@ def logits(logits_t: torch.Tensor, logp_old, logp_ref, selected, advantages, wei
 def _order_ptr(row_order, n_rows: int):
     if row_order is None:
         return None
-    if row_order.numel() != n_rows + 2:
+    if row_order.numel() != _lib.lib().grpo_b200_row_order_bytes(n_rows) // 4:
         raise ValueError("row_order must come from row_order() on a mask over the same rows")
     return _check_tensor(row_order, torch.int32, "row_order")
 
 
 def row_order(mask: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``[n_active, n_masked, active rows..., masked rows...]`` (int32, ``len(mask) + 2``): the stable
-    partition of the local row indices by ``mask`` that :func:`logits` takes as ``row_order``."""
+    """``[n_active, n_masked, active rows..., masked rows...]`` (int32, ``len(mask) + 2`` entries and a
+    scratch tail): the stable partition of the local row indices by ``mask`` that :func:`logits`
+    takes as ``row_order``."""
     m = _check_tensor(mask, torch.int32, "mask")
     if out is None:
-        out = torch.empty(mask.numel() + 2, dtype=torch.int32, device=mask.device)
+        out = torch.empty(_lib.lib().grpo_b200_row_order_bytes(mask.numel()) // 4, dtype=torch.int32,
+                          device=mask.device)
     _lib.check(_lib.lib().grpo_b200_row_order(m, mask.numel(), _check_tensor(out, torch.int32, "row_order"), _stream()))
     return out
 

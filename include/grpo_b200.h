@@ -194,7 +194,8 @@ int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
                      grpo_b200_stream_t stream);
 
 /* Stable partition of the local row indices by mask, for the row_order argument above:
- * order[n_rows + 2] = {n_active, n_masked, active rows ascending, masked rows ascending}.
+ * order = {n_active, n_masked, active rows ascending, masked rows ascending}, n_rows + 2
+ * entries, in a buffer of grpo_b200_row_order_bytes(n_rows) (the tail is scratch).
  * No counterpart in the reference (its kernels take one row per block, in index order,
  * src/cuda/grpo_loss_cuda.cu:551-582).  Depends on the mask only: computed once per batch. */
 size_t grpo_b200_row_order_bytes(int64_t n_rows);

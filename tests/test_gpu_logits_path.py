@@ -373,7 +373,7 @@ def test_row_order_partition_and_invariance():
     rng = np.random.default_rng(8)
     for n in (1, 31, 1024, 70001):
         m = (rng.random(n) < 0.6).astype(np.int32)
-        got = D.row_order(torch.from_numpy(m).cuda()).cpu().numpy()
+        got = D.row_order(torch.from_numpy(m).cuda()).cpu().numpy()[: n + 2]
         idx = np.arange(n, dtype=np.int32)
         want = np.concatenate(([m.sum(), n - m.sum()], idx[m != 0], idx[m == 0])).astype(np.int32)
         assert (got == want).all()
