@@ -251,7 +251,7 @@ def gpu_arm(args, spec: dict) -> None:
     S, N = B * Gn, B * Gn * T
     mask_h, sel_h, adv_h, noise_old, noise_ref = host_metadata(spec)
     # contiguous row ranges of equal kernel time (ragged masks make equal row counts unequal work)
-    off, cnt = shard_rows_balanced(mask_h, world, V, P)[rank]
+    off, cnt = shard_rows_balanced(mask_h, world, V, P, args.masked_cost)[rank]
     sl = slice(off, off + cnt)
 
     # ---- this rank's rows, built on the device
@@ -325,7 +325,15 @@ def gpu_arm(args, spec: dict) -> None:
 
     sb.prepare(devt["mask"])  # weights for the first pass; every later pass gets them from the pass before
 
+    align = torch.zeros(1, device=dev)
+
     def timed_pass(e0, e1):
+        # The restore above takes a different time on every rank (the ranks hold different numbers of rows), and a
+        # rank that starts its pass late makes the others wait inside their timed exchange.  A one-element
+        # all-reduce, enqueued like everything else and outside the event pair, lines the ranks up first, so the
+        # pair measures the pass itself: slowest rank's kernels plus the exchange.
+        if world > 1:
+            dist.all_reduce(align)
         e0.record()
         if graph is not None:
             graph.replay()
@@ -363,9 +371,14 @@ def gpu_arm(args, spec: dict) -> None:
     stats = sb.stats()  # applies the error contract to the global quantities
 
     total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
+    per_rank = torch.zeros(world, 2, dtype=torch.float64, device=dev)  # [rank] = (pass ms, dominant kernel ms)
+    per_rank[rank, 0] = sum(step_ms) / len(step_ms)
+    per_rank[rank, 1] = statistics.mean(kern_ms)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(per_rank)
     total_ms = float(total_ms.item())
+    per_rank = per_rank.cpu().tolist()
 
     # ---- end to end through the public API with host metadata --------------------------------
     h2d = sum(host[k].numel() * host[k].element_size() for k in host)
@@ -421,6 +434,7 @@ def gpu_arm(args, spec: dict) -> None:
             "active_tokens_per_s": int(mask_h.sum()) * args.steps / (total_ms * 1e-3),
             "loss": stats["loss"], "valid_tokens": stats["valid_tokens"],
             "wall_s_timed_loop": t_wall,
+            "per_rank_ms": {"pass": [round(p, 4) for p, _ in per_rank], "kernel": [round(k, 4) for _, k in per_rank]},
             "clocks": clocks,
             "e2e": {"value": N * args.steps / e2e_total, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 48, "ms_per_step": 1e3 * e2e_total / args.steps,
@@ -469,6 +483,8 @@ def main() -> None:
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="at more than one rank: the pass's exchange by the library's own kernel over NVLink peer "
                          "memory, or by one NCCL all-reduce")
+    ap.add_argument("--masked-cost", type=float, default=0.8,
+                    help="cost of a masked row in units of P floats when cutting the batch into per-rank row ranges")
     ap.add_argument("--no-graph", action="store_true", help="launch each pass eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     import grpo_cpp_b200  # noqa: F401  (registers the package under its importable name)
