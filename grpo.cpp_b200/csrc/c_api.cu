@@ -256,7 +256,7 @@ int grpo_b200_row_order(const int32_t* mask, int64_t n_rows, int32_t* order, grp
 
 size_t grpo_b200_exchange_bytes(int64_t n_seq) {
     if (n_seq <= 0) return 0;
-    return exchange_counts_offset(n_seq) + static_cast<size_t>(n_seq) * sizeof(int32_t);
+    return exchange_lengths_offset(n_seq) + static_cast<size_t>(n_seq) * sizeof(double);
 }
 
 int grpo_b200_exchange_create(int64_t n_seq, void** region) {

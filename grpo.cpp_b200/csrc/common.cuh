@@ -213,16 +213,21 @@ struct LogitsArgs {
     double* partials;   // [ceil(n_rows / 256)][5] per-block sums of the reduce kernel
 };
 
-// The exchange region of one rank (device memory that every rank of the box maps): a header of
-// sequence numbers flags[2][8] and the region's own pass counter, then slots[2][8][stride] doubles
-// ([buffer = pass & 1][source rank]), then counts[n_seq] int32, this rank's valid-token counts for
-// the next pass (zero between passes: the kernel that reads them clears them).
+// The exchange region of one rank (device memory that every rank of the box maps): a header with
+// the region's own pass counter; slots[2][8][stride][2] 8-byte words ([buffer = pass & 1][source
+// rank][element][half]), each word = 32 bits of a double in the low half and the pass number in
+// the high half; counts[n_seq] int32, this rank's valid-token counts for the next pass (zero
+// between passes: the kernel that reads them clears them); lengths[n_seq] doubles, the global
+// counts of the last exchange.
 constexpr int kExchangeMaxWorld = 8;
 constexpr int kExchangePassOffset = 128;
 constexpr int kExchangeHeaderBytes = 256;
 __host__ __device__ inline long long exchange_stride(long long n_seq) { return (5 + n_seq + 1) & ~1LL; }
 __host__ __device__ inline size_t exchange_counts_offset(long long n_seq) {
-    return kExchangeHeaderBytes + static_cast<size_t>(2 * kExchangeMaxWorld) * exchange_stride(n_seq) * sizeof(double);
+    return kExchangeHeaderBytes + static_cast<size_t>(2 * kExchangeMaxWorld) * exchange_stride(n_seq) * 16;
+}
+__host__ __device__ inline size_t exchange_lengths_offset(long long n_seq) {
+    return exchange_counts_offset(n_seq) + ((static_cast<size_t>(n_seq) * sizeof(int32_t) + 15) & ~static_cast<size_t>(15));
 }
 
 struct ExchangeArgs {

@@ -893,18 +893,16 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
 //    slots in index order, so the totals depend on the row count only, never on scheduling.
 // 3. Sharded runs: the same block then carries out the pass's only exchange itself.  It writes
 //    the record, followed by this rank's counts, into its slot of every rank's exchange region
-//    over NVLink, publishes a per-slot sequence number with a system-scope release, waits
-//    (bounded) for the other ranks' numbers, adds the slots in rank order -- the same bits on
-//    every rank -- and derives the next pass's weights from the global counts.  A non-zero
+//    over NVLink -- 8-byte words that carry the pass number next to 32 bits of data, so no fence
+//    and no separate flag -- polls (bounded) its own region until every rank's words show this
+//    pass's number, adds the slots in rank order -- the same bits on every rank -- and derives
+//    the next pass's weights from the global counts.  A non-zero
 //    status word (a pipeline wait timed out) turns bad_inputs into -1, an exchange that timed
 //    out into -2.
 constexpr int kReduceThreads = 256;
 
-__device__ __forceinline__ unsigned long long* exchange_flag(unsigned char* region, int buf, int src) {
-    return reinterpret_cast<unsigned long long*>(region) + buf * kExchangeMaxWorld + src;
-}
-__device__ __forceinline__ double* exchange_slot(unsigned char* region, long long stride, int buf, int src) {
-    return reinterpret_cast<double*>(region + kExchangeHeaderBytes) + (buf * kExchangeMaxWorld + src) * stride;
+__device__ __forceinline__ unsigned long long* exchange_slot(unsigned char* region, long long stride, int buf, int src) {
+    return reinterpret_cast<unsigned long long*>(region + kExchangeHeaderBytes) + (buf * kExchangeMaxWorld + src) * stride * 2;
 }
 
 __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const LogitsArgs a, const ExchangeArgs x) {
@@ -995,8 +993,12 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
     if (x.world <= 0) return;
     __syncthreads();
 
-    // ---- the exchange: push (clearing the counts for the next pass), publish, wait, add
+    // ---- the exchange: push (clearing the counts for the next pass), poll, add.  Every double
+    //      travels as two 8-byte words, each carrying 32 bits of it next to the pass number: an
+    //      8-byte store arrives whole, so a word that shows this pass's number is this pass's
+    //      data and no fence or separate flag is needed.
     const unsigned long long seq = pass_sh;
+    const unsigned long long tag = (seq & 0xffffffffULL) << 32;  // never zero-matching: the region starts zeroed, seq >= 1
     const int buf = static_cast<int>(seq & 1ULL);
     const long long n = 5 + x.n_seq;
     const long long stride = exchange_stride(x.n_seq);
@@ -1009,49 +1011,48 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
             mine = static_cast<double>(__ldcg(counts + (i - 5)));
             counts[i - 5] = 0;
         }
-        for (int p = 0; p < x.world; p++) exchange_slot(x.peers[p], stride, buf, x.rank)[i] = mine;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < x.world) {
-        unsigned long long* theirs = exchange_flag(x.peers[tid], buf, x.rank);
-        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(theirs), "l"(seq) : "memory");
-        const unsigned long long* mine = exchange_flag(x.peers[x.rank], buf, tid);
-        const long long start = clock64();
-        for (;;) {
-            unsigned long long seen;
-            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
-            if (seen == seq) break;
-            if (clock64() - start > (1LL << 32)) {  // about two seconds: a peer is gone
-                timed_out = 1;
-                break;
-            }
-            __nanosleep(64);
+        const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(mine));
+        const unsigned long long w0 = (bits & 0xffffffffULL) | tag, w1 = (bits >> 32) | tag;
+        for (int p = 0; p < x.world; p++) {
+            unsigned long long* dst = exchange_slot(x.peers[p], stride, buf, x.rank) + 2 * i;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(w0) : "memory");
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + 1), "l"(w1) : "memory");
         }
     }
-    __syncthreads();
-    // the global counts are written over this rank's own slot of this buffer (thread i is the only reader of
-    // element i, and nobody else writes the slot), where the weights step below reads them
     double* out = reinterpret_cast<double*>(a.result);
-    double* global_lengths = exchange_slot(x.peers[x.rank], stride, buf, x.rank) + 5;
+    double* global_lengths = reinterpret_cast<double*>(x.peers[x.rank] + exchange_lengths_offset(x.n_seq));
+    const long long start = clock64();
     for (long long i = tid; i < n; i += kReduceThreads) {
         double s = 0.0;
         bool negative = false;
         for (int q = 0; q < x.world; q++) {
-            const double term = __ldcv(exchange_slot(x.peers[x.rank], stride, buf, q) + i);
+            const unsigned long long* src = exchange_slot(x.peers[x.rank], stride, buf, q) + 2 * i;
+            unsigned long long w0, w1;
+            for (;;) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w0) : "l"(src) : "memory");
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w1) : "l"(src + 1) : "memory");
+                if ((w0 & 0xffffffff00000000ULL) == tag && (w1 & 0xffffffff00000000ULL) == tag) break;
+                if (timed_out || clock64() - start > (1LL << 32)) {  // about two seconds: a peer is gone
+                    timed_out = 1;
+                    w0 = w1 = 0ULL;
+                    break;
+                }
+                __nanosleep(32);
+            }
+            const double term = __longlong_as_double(static_cast<long long>((w0 & 0xffffffffULL) | (w1 << 32)));
             negative = negative || term < 0.0;
             s += term;
         }
         if (i < 5) {
-            if (i == 4 && negative) s = -1.0;   // some rank's pipeline gave up
-            if (i == 4 && timed_out) s = -2.0;  // some rank never answered
-            out[i] = s;
+            if (i == 4 && negative) s = -1.0;  // some rank's pipeline gave up
+            record[i] = s;
         } else {
             global_lengths[i - 5] = s;
             if (x.lengths_out) x.lengths_out[i - 5] = s;
         }
     }
     __syncthreads();
+    if (tid < 5) out[tid] = (tid == 4 && timed_out) ? -2.0 : record[tid];  // -2: some rank never answered
     block_weights<kReduceThreads>(global_lengths, x.n_seq, x.reduction, x.length_alpha, x.weights_out, x.meta_out,
                                   scratch);
 }
