@@ -47,6 +47,44 @@ int check_options(float clip_eps, float beta) {
 constexpr long long kIntMax = 2147483647LL;
 
 }  // namespace
+
+// The selected-token pass.  `kept_counter` is a ticket counter that is zero now and that the kernel
+// leaves at zero (the library's own per-device buffers keep one); without it the counter at the end
+// of the caller's workspace is used and cleared first, which costs one more stream operation.
+int loss_pass(const float* logp_new, const float* logp_old, const float* logp_ref, const float* advantages,
+              const float* weights, const int32_t* mask, int64_t n_tokens, int64_t token_offset, int tokens_per_seq,
+              float clip_eps, float beta, float* dlogp, grpo_b200_result_t* result, void* workspace,
+              size_t workspace_bytes, unsigned* kept_counter, grpo_b200_stream_t stream) {
+    if (!logp_new || !logp_old || !logp_ref || !advantages || !weights || !mask || !dlogp || !result)
+        return invalid("device pointers must not be null");
+    if (n_tokens <= 0 || tokens_per_seq <= 0 || token_offset < 0) return invalid("B, G and T must be positive");
+    if (token_offset + n_tokens > kIntMax) return invalid("token count exceeds INT_MAX");
+    if (int rc = check_options(clip_eps, beta)) return rc;
+    if (!workspace || workspace_bytes < grpo_b200_loss_workspace_bytes(n_tokens) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 7u)) {
+        set_error("workspace must be 8-byte aligned and hold grpo_b200_loss_workspace_bytes() bytes");
+        return GRPO_B200_E_WORKSPACE;
+    }
+    LossArgs a;
+    a.logp_new = logp_new;
+    a.logp_old = logp_old;
+    a.logp_ref = logp_ref;
+    a.advantages = advantages;
+    a.weights = weights;
+    a.mask = mask;
+    a.n_tokens = n_tokens;
+    a.token_offset = token_offset;
+    a.tokens_per_seq = tokens_per_seq;
+    a.clip_eps = clip_eps;
+    a.beta = beta;
+    a.dlogp = dlogp;
+    a.result = result;
+    a.partials = static_cast<double*>(workspace);
+    a.counter = kept_counter ? kept_counter : reinterpret_cast<unsigned*>(a.partials + 2048 * 5);
+    GRPO_CUDA_TRY(launch_loss(a, kept_counter == nullptr, reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
 }  // namespace grpo_b200
 
 using namespace grpo_b200;
@@ -128,34 +166,8 @@ int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* lo
                    const float* weights, const int32_t* mask, int64_t n_tokens, int64_t token_offset,
                    int tokens_per_seq, float clip_eps, float beta, float* dlogp, grpo_b200_result_t* result,
                    void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream) {
-    if (!logp_new || !logp_old || !logp_ref || !advantages || !weights || !mask || !dlogp || !result)
-        return invalid("device pointers must not be null");
-    if (n_tokens <= 0 || tokens_per_seq <= 0 || token_offset < 0) return invalid("B, G and T must be positive");
-    if (token_offset + n_tokens > kIntMax) return invalid("token count exceeds INT_MAX");
-    if (int rc = check_options(clip_eps, beta)) return rc;
-    if (!workspace || workspace_bytes < grpo_b200_loss_workspace_bytes(n_tokens) ||
-        (reinterpret_cast<uintptr_t>(workspace) & 7u)) {
-        set_error("workspace must be 8-byte aligned and hold grpo_b200_loss_workspace_bytes() bytes");
-        return GRPO_B200_E_WORKSPACE;
-    }
-    LossArgs a;
-    a.logp_new = logp_new;
-    a.logp_old = logp_old;
-    a.logp_ref = logp_ref;
-    a.advantages = advantages;
-    a.weights = weights;
-    a.mask = mask;
-    a.n_tokens = n_tokens;
-    a.token_offset = token_offset;
-    a.tokens_per_seq = tokens_per_seq;
-    a.clip_eps = clip_eps;
-    a.beta = beta;
-    a.dlogp = dlogp;
-    a.result = result;
-    a.partials = static_cast<double*>(workspace);
-    a.counter = reinterpret_cast<unsigned*>(a.partials + 2048 * 5);
-    GRPO_CUDA_TRY(launch_loss(a, reinterpret_cast<cudaStream_t>(stream)));
-    return GRPO_B200_OK;
+    return loss_pass(logp_new, logp_old, logp_ref, advantages, weights, mask, n_tokens, token_offset, tokens_per_seq,
+                     clip_eps, beta, dlogp, result, workspace, workspace_bytes, nullptr, stream);
 }
 
 size_t grpo_b200_logits_workspace_bytes(int64_t n_rows) {

@@ -177,7 +177,11 @@ struct LossArgs {
     unsigned* counter;  // ticket counter of the blocks (cleared before the launch); unused by the two-launch form
 };
 int loss_grid_blocks(long long n_tokens);
-cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream);
+cudaError_t launch_loss(const LossArgs& a, bool clear_counter, cudaStream_t stream);
+int loss_pass(const float* logp_new, const float* logp_old, const float* logp_ref, const float* advantages,
+              const float* weights, const int32_t* mask, int64_t n_tokens, int64_t token_offset, int tokens_per_seq,
+              float clip_eps, float beta, float* dlogp, grpo_b200_result_t* result, void* workspace,
+              size_t workspace_bytes, unsigned* kept_counter, grpo_b200_stream_t stream);
 
 // What the row kernels leave per active row for the reduce kernel: the normaliser (relative to
 // e^m, double), the row maximum, the gathered selected logit and the input-error flags.  The

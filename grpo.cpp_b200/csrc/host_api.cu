@@ -43,8 +43,15 @@ struct Arena {
     char* pinned = nullptr;
     size_t pinned_cap = 0;
     cudaEvent_t ev[2] = {nullptr, nullptr};
+    unsigned* ticket = nullptr;  // zero between calls: the selected-token kernel's ticket counter
 
     cudaError_t reserve(size_t dev_bytes, size_t pinned_bytes) {
+        if (!ticket) {
+            cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&ticket), 256);
+            if (err != cudaSuccess) return err;
+            err = cudaMemset(ticket, 0, 256);
+            if (err != cudaSuccess) return err;
+        }
         if (dev_bytes > dev_cap) {
             if (dev) cudaFree(dev);
             dev = nullptr;
@@ -74,6 +81,8 @@ struct Arena {
     void release_memory() {
         if (dev) cudaFree(dev);
         if (pinned) cudaFreeHost(pinned);
+        if (ticket) cudaFree(ticket);
+        ticket = nullptr;
         dev = pinned = nullptr;
         dev_cap = pinned_cap = 0;
     }
@@ -342,8 +351,8 @@ int grpo_b200_loss_host(const float* logp_new, size_t n_logp_new, const float* l
     GRPO_CUDA_TRY(cudaMemcpyAsync(old_d, logp_old, n * 4, cudaMemcpyHostToDevice, nullptr));
     GRPO_CUDA_TRY(cudaMemcpyAsync(ref_d, logp_ref, n * 4, cudaMemcpyHostToDevice, nullptr));
     GRPO_CUDA_TRY(cudaMemcpyAsync(mask_d, mask, n * 4, cudaMemcpyHostToDevice, nullptr));
-    if (int rc = grpo_b200_loss(new_d, old_d, ref_d, adv_d, w_d, mask_d, static_cast<int64_t>(n), 0, T, clip_eps,
-                                beta, dlogp_d, result_d, work_d, work_bytes, nullptr))
+    if (int rc = loss_pass(new_d, old_d, ref_d, adv_d, w_d, mask_d, static_cast<int64_t>(n), 0, T, clip_eps, beta,
+                           dlogp_d, result_d, work_d, work_bytes, arena.ticket, nullptr))
         return rc;
     GRPO_CUDA_TRY(cudaMemcpyAsync(result_h, result_d, sizeof(*result_h), cudaMemcpyDeviceToHost, nullptr));
     GRPO_CUDA_TRY(cudaMemcpyAsync(dlogp_out, dlogp_d, n * 4, cudaMemcpyDeviceToHost, nullptr));
@@ -504,8 +513,8 @@ int grpo_b200_benchmark_loss_host(const float* logp_new, size_t n_logp_new, cons
     GRPO_CUDA_TRY(cudaMemcpy(w_d, weights.data(), s * 4, cudaMemcpyHostToDevice));
 
     auto pass = [&]() {
-        return grpo_b200_loss(new_d, old_d, ref_d, adv_d, w_d, mask_d, static_cast<int64_t>(n), 0, T, clip_eps, beta,
-                              dlogp_d, result_d, work_d, work_bytes, nullptr);
+        return loss_pass(new_d, old_d, ref_d, adv_d, w_d, mask_d, static_cast<int64_t>(n), 0, T, clip_eps, beta,
+                         dlogp_d, result_d, work_d, work_bytes, arena.ticket, nullptr);
     };
     for (int i = 0; i < 2 * warmup; i++)
         if (int rc = pass()) return rc;

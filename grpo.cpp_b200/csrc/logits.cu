@@ -5,37 +5,45 @@
 // (src/cuda/grpo_loss_cuda.cu:181-349).  Two kernels live here.
 //
 // PIPELINED kernel (what GRPO_B200_LOGITS_FUSED runs whenever the layout allows):
-//   * persistent: one CTA per SM (or a thread-block cluster of 2/4/8 CTAs for rows that do not
-//     fit one CTA's registers) walks rows cluster_id, cluster_id + n_clusters, ...;
+//   * persistent: thread-block clusters of 1/2/4/8 small CTAs (four CTAs of 128 consumer threads
+//     per SM for the common widths, so that one CTA's serial phases overlap the others' work)
+//     walk the rows, every cluster taking every n-th active and every n-th masked row when the
+//     caller supplies the row order, else every n-th row;
 //   * a ring of shared-memory stages is filled by bulk asynchronous copies
-//     (cp.async.bulk global -> shared, completion on an mbarrier) issued by one elected thread
-//     up to STAGES tiles ahead, so the next rows stream in from HBM while the current row is
+//     (cp.async.bulk global -> shared, completion on an mbarrier) issued by a dedicated producer
+//     warp up to STAGES tiles ahead, so the next rows stream in from HBM while the current row is
 //     being reduced and written back -- the copy engine, not thread occupancy, hides latency;
 //   * each thread lifts its chunks from the ring into registers (128-bit LDS), releases the
 //     stage, and keeps the row slice in registers until the gradient is stored (128-bit
 //     streaming stores): one HBM read and one HBM write per logit, one exp per element;
-//   * the row reduction runs registers -> warp shuffles -> shared memory -> distributed shared
-//     memory across the cluster; no global atomics.
+//   * the row reduction runs registers -> warp shuffles -> one 32-byte partial per warp sent
+//     with st.async into the shared memory of every CTA of the cluster, counted on that CTA's
+//     mbarrier; warp 0 of every CTA combines all partials in slot order.  No global atomics.
 //   Every bulk copy has a single destination CTA (its issuer).
 //
 // STREAMING kernel (GRPO_B200_LOGITS_SEPARATE, and any layout the pipelined kernel cannot take:
 // P not a multiple of 4, unaligned base, rows beyond the largest cluster): one CTA per row,
 // sweeps over global memory (max, normaliser, correction, gradient), later sweeps from L2.
 //
+// REDUCE kernel (second and last launch of a pass): per-row loss terms in double, fixed-order
+// totals by the block that takes the last ticket, and, in sharded runs, the exchange between the
+// ranks and the next pass's weights.
+//
 // Accuracy of the log-sum-exp.  The token loss is a cancelling sum and the reference rounds
 // log p(selected) to fp32, so the normaliser has to agree with the reference's double
-// arithmetic to about 1e-8 relative or rows round differently.  Both kernels therefore
+// arithmetic to about 1e-8 relative or rows round differently.  Both row kernels therefore
 //   (1) evaluate e_i = 2^(x_i*log2e - shift) with a two-constant log2e and one FMA residual so
 //       the exponent itself carries no systematic error,
-//   (2) accumulate the e_i in double (fixed trees), combining per-warp partial sums with
-//       factors computed in double, and
-//   (3) recompute in double the few elements that each carry more than 1/256 of the
-//       normaliser (at most 256 per row; none when the row is flat) and correct the sum.
+//   (2) sum the e_i exactly (compensated fp32 chains, or double), combining per-warp partial
+//       sums with factors computed in double and scaling by the measured mean error of the
+//       hardware ex2, and
+//   (3) recompute in double the elements that can each carry a visible share of the normaliser
+//       (every thread's two largest in the pipelined kernel; those above 1/256 of it in the
+//       streaming kernel) and correct the sum.
 // The gradient itself only needs the fp32 e_i.
 //
-// Neither kernel touches a masked row's logits or selected id; both write zeros over all P
-// columns of a masked row and over columns [V, P) of an active one.  Per-row loss terms go to a
-// workspace and are summed in a fixed order by the reduce kernel.
+// Neither row kernel touches a masked row's logits or selected id; both write zeros over all P
+// columns of a masked row and over columns [V, P) of an active one.
 #include <cooperative_groups.h>
 
 #include "common.cuh"

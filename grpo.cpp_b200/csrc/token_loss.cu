@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(THREADS) token_loss_kernel(const LossArgs a) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    if (threadIdx.x == 0) *a.counter = 0u;  // every ticket is taken: the counter is left as it was found
     double v[kPartialWidth];
 #pragma unroll
     for (int k = 0; k < kPartialWidth; k++) v[k] = 0.0;
@@ -316,12 +317,14 @@ int loss_grid_blocks(long long n_tokens) {
     return static_cast<int>(blocks);
 }
 
-cudaError_t launch_loss(const LossArgs& a, cudaStream_t stream) {
+cudaError_t launch_loss(const LossArgs& a, bool clear_counter, cudaStream_t stream) {
     const bool vec = aligned16(a.logp_new) && aligned16(a.logp_old) && aligned16(a.logp_ref) &&
                      aligned16(a.mask) && aligned16(a.dlogp);
     const int blocks = loss_grid_blocks(a.n_tokens);
-    cudaError_t err = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), stream);
-    if (err != cudaSuccess) return err;
+    if (clear_counter) {
+        cudaError_t err = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), stream);
+        if (err != cudaSuccess) return err;
+    }
     if (vec)
         token_loss_kernel<true, kLossThreads, true><<<blocks, kLossThreads, 0, stream>>>(a);
     else
