@@ -138,3 +138,38 @@ def test_workload_shapes():
     assert t.N == 1024 and t.logp_new.max() <= 0 and t.logp_new.min() >= np.log(0.01) - 1e-6
     s = W.GPT2_SHAPE
     assert s["B"] * s["G"] * s["T"] == 65536 and s["P"] % 4 == 0 and s["P"] >= s["V"]
+
+
+def test_sharded_entry_point_validation_needs_no_device():
+    """grpo_b200_logits_sharded, grpo_b200_row_order and the exchange-region calls reject bad
+    arguments before they touch the device; fake non-null pointers are never dereferenced."""
+    import ctypes as C
+    from grpo_cpp_b200 import _lib
+    L = _lib.lib()
+    p = C.c_void_p(4096)
+    regions = (C.c_void_p * 8)(*([4096] * 8))
+
+    def sharded(world=2, rank=0, n_seq=4, next_mask=p, reduction=1, regs=regions, n_rows=8, T=2):
+        return L.grpo_b200_logits_sharded(p, p, p, p, p, p, p, p, n_rows, 0, T, 16, 16, 0.2, 0.01, 1, 0, None, None,
+                                          p, p, 1 << 20, regs, rank, world, n_seq, next_mask, reduction, 0.0, p, p,
+                                          None, None)
+
+    for kw, msg in ((dict(world=9), "world must lie in [1, 8]"), (dict(world=0), "world must lie in [1, 8]"),
+                    (dict(rank=2), "rank must lie in [0, world)"),
+                    (dict(next_mask=None), "regions, next_mask, next_weights and next_meta must not be null and "
+                                           "n_seq must be positive"),
+                    (dict(n_seq=0), "regions, next_mask, next_weights and next_meta must not be null and "
+                                    "n_seq must be positive"),
+                    (dict(reduction=3), "unknown reduction mode"),
+                    (dict(n_seq=3), "rows reach beyond the last response"),
+                    (dict(regs=(C.c_void_p * 8)(4096, None)), "every rank's exchange region must be mapped")):
+        assert sharded(**kw) == 1, kw
+        assert _lib.last_error() == msg
+    assert L.grpo_b200_row_order(None, 8, p, None) == 1 and _lib.last_error() == "device pointers must not be null"
+    assert L.grpo_b200_row_order(p, 0, p, None) == 1 and _lib.last_error() == "n_rows must lie in [1, INT_MAX]"
+    assert L.grpo_b200_row_order_bytes(2048) == (2048 + 2 + 2) * 4
+    assert L.grpo_b200_exchange_bytes(0) == 0 and L.grpo_b200_exchange_bytes(256) > 2 * 8 * 261 * 16
+    assert L.grpo_b200_exchange_create(0, C.byref(C.c_void_p())) == 1
+    assert L.grpo_b200_exchange_export(None, C.create_string_buffer(64)) == 1
+    assert L.grpo_b200_exchange_open(None, C.byref(C.c_void_p())) == 1
+    assert L.grpo_b200_exchange_close(None) == 0 and L.grpo_b200_exchange_destroy(None) == 0
