@@ -352,6 +352,21 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                        workspace, workspace_bytes, x, stream);
 }
 
+int grpo_b200_sample_rows(const float* logits, int64_t n_rows, int V, int P, const int32_t* rows, int n_selected,
+                          const double* coins, const int32_t* given_tokens, int32_t* tokens_out, float* logp_out,
+                          double* lse_out, grpo_b200_stream_t stream) {
+    if (!logits || !rows) return invalid("device pointers must not be null");
+    if (n_rows <= 0 || n_rows > kIntMax) return invalid("n_rows must lie in [1, INT_MAX]");
+    if (V <= 0) return invalid("V must be positive");
+    if (P < V) return invalid("P must be at least V");
+    if (n_selected <= 0) return invalid("n_selected must be positive");
+    if ((coins == nullptr) == (given_tokens == nullptr)) return invalid("pass either coins or given_tokens");
+    if (coins && !tokens_out) return invalid("tokens_out must not be null when tokens are drawn");
+    GRPO_CUDA_TRY(launch_sample_rows(logits, n_rows, V, P, rows, n_selected, coins, given_tokens, tokens_out, logp_out,
+                                     lse_out, reinterpret_cast<cudaStream_t>(stream)));
+    return GRPO_B200_OK;
+}
+
 int grpo_b200_logits_set_variant(int variant) {
     if (variant >= resident_variant_count()) return invalid("no such kernel variant");
     g_forced_variant = variant < 0 ? -1 : variant;

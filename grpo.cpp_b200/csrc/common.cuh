@@ -267,6 +267,9 @@ cudaError_t launch_count_lengths_f64(const int32_t* mask, long long n_rows, long
                                      int tokens_per_seq, long long n_seq, double* lengths, cudaStream_t stream);
 cudaError_t launch_weights_f64(const double* lengths, long long n_seq, int reduction, float alpha,
                                float* weights, int32_t* meta, cudaStream_t stream);
+cudaError_t launch_sample_rows(const float* logits, long long n_rows, int V, int P, const int32_t* rows, int n_sel,
+                               const double* coins, const int32_t* given, int32_t* tokens_out, float* logp_out,
+                               double* lse_out, cudaStream_t stream);
 cudaError_t launch_row_order(const int32_t* mask, long long n_rows, int32_t* order, cudaStream_t stream);
 cudaError_t launch_group_advantages(const float* rewards, int B, int G, int mode, float eps,
                                     float* advantages, int32_t* meta, cudaStream_t stream);

@@ -264,6 +264,26 @@ def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advanta
     return result
 
 
+def sample_rows(logits_t: torch.Tensor, V: int, rows: torch.Tensor, *, coins: torch.Tensor | None = None,
+                tokens: torch.Tensor | None = None):
+    """For the rows of ``logits_t`` (``[n_rows, P]`` fp32) named in ``rows`` (int32): the row
+    log-sum-exp (float64), a token per row -- drawn by inverse CDF from ``coins`` (float64 uniforms in
+    [0, 1)) or taken from ``tokens`` (int32) -- and its fp32 log-probability.  Returns
+    ``(tokens, logp, lse)``; nothing but these few numbers needs to leave the device."""
+    n_rows, P = logits_t.shape
+    n = rows.numel()
+    dev = logits_t.device
+    out_tokens = torch.empty(n, dtype=torch.int32, device=dev) if coins is not None else None
+    logp = torch.empty(n, dtype=torch.float32, device=dev)
+    lse = torch.empty(n, dtype=torch.float64, device=dev)
+    _lib.check(_lib.lib().grpo_b200_sample_rows(
+        _check_tensor(logits_t, torch.float32, "logits"), n_rows, V, P, _check_tensor(rows, torch.int32, "rows"), n,
+        None if coins is None else _check_tensor(coins, torch.float64, "coins"),
+        None if tokens is None else _check_tensor(tokens, torch.int32, "tokens"),
+        None if out_tokens is None else out_tokens.data_ptr(), logp.data_ptr(), lse.data_ptr(), _stream()))
+    return (out_tokens if coins is not None else tokens), logp, lse
+
+
 def set_variant(variant: int) -> None:
     """Force a row-resident kernel variant (index into :func:`variants`), ``-1`` for automatic."""
     _lib.check(_lib.lib().grpo_b200_logits_set_variant(variant))

@@ -241,6 +241,24 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                              float length_alpha, float* next_weights, int32_t* next_meta,
                              double* next_lengths, grpo_b200_stream_t stream);
 
+/* Sampling and log-probability extraction on logits that stay on the device.  Replaces, for
+ * the rows named in rows[n_selected] (indices into the [n_rows][P] logits), the host-side
+ * row_logsumexp / sample_row / draw_sample of apps/04_gpt2_grpo.cu:61-80,138-161, which need
+ * the whole logits array copied to the host (copy_logits, :82-90):
+ *   lse   = max + log(sum_v exp((double)(x_v - max)))
+ *   token = coins ? first v with coins[i] < sum_{u<=v} exp((double)x_u - lse), else V-1
+ *                 : given_tokens[i]
+ *   logp  = (float)((double)x_token - lse)        (0 when a given token is outside [0, V))
+ * Exactly one of coins (uniform numbers in [0,1), drawn by the caller's generator) and
+ * given_tokens is non-null: draw under the policy's logits with coins, then read the same tokens'
+ * log-probabilities under the reference model's logits with given_tokens.  tokens_out, logp_out
+ * and lse_out are device arrays of n_selected entries (logp_out, lse_out, and tokens_out when
+ * tokens are given, may be null).  A row index outside [0, n_rows) yields token -1, a NaN lse. */
+int grpo_b200_sample_rows(const float* logits, int64_t n_rows, int V, int P, const int32_t* rows,
+                          int n_selected, const double* coins, const int32_t* given_tokens,
+                          int32_t* tokens_out, float* logp_out, double* lse_out,
+                          grpo_b200_stream_t stream);
+
 /* Tuning hook for benchmarks: force the row-resident kernel variant (index into the table
  * printed by grpo_b200_logits_variant_name), or -1 for the built-in choice.  Process-wide. */
 int grpo_b200_logits_set_variant(int variant);

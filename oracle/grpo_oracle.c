@@ -250,3 +250,24 @@ done:
     free(dlogp);
     return rc;
 }
+
+/* apps/04_gpt2_grpo.cu:61-66 */
+double grpo_oracle_row_logsumexp(const float* row, int V) {
+    float top = row[0];
+    for (int v = 1; v < V; v++)
+        if (row[v] > top) top = row[v];
+    double sum = 0.0;
+    for (int v = 0; v < V; v++) sum += exp((double)(row[v] - top));
+    return (double)top + log(sum);
+}
+
+/* apps/04_gpt2_grpo.cu:68-80 */
+int grpo_oracle_sample_row(const float* row, int V, double coin) {
+    double lse = grpo_oracle_row_logsumexp(row, V);
+    double cumulative = 0.0;
+    for (int v = 0; v < V; v++) {
+        cumulative += exp((double)row[v] - lse);
+        if (coin < cumulative) return v;
+    }
+    return V - 1;
+}

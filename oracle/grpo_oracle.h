@@ -75,6 +75,14 @@ int grpo_oracle_logits(const float* logits, const float* logp_old, const float* 
                        float* dlogits_out, float* stats_out, int* valid_tokens_out,
                        float* selected_logp_out);
 
+/* Sampling helpers of the reference's GPT-2 demo, restated: apps/04_gpt2_grpo.cu:61-66
+ * (row_logsumexp) and :68-80 (sample_row, with the uniform number passed in instead of drawn
+ * from std::mt19937 inside).  Parity of these two: UNPINNED -- the demo is one translation unit
+ * with the absent llm.c model code, so its object code cannot be built here, and the reference
+ * has no test or golden vector for them; they are pinned by known answers only. */
+double grpo_oracle_row_logsumexp(const float* row, int V);
+int grpo_oracle_sample_row(const float* row, int V, double coin);
+
 #ifdef __cplusplus
 }
 #endif

@@ -80,6 +80,10 @@ class _Lib:
         if kind == "port":
             self.lib.grpo_oracle_strerror.restype = C.c_char_p
             self.lib.grpo_oracle_strerror.argtypes = [C.c_int]
+            self.lib.grpo_oracle_row_logsumexp.restype = C.c_double
+            self.lib.grpo_oracle_row_logsumexp.argtypes = [_fp, C.c_int]
+            self.lib.grpo_oracle_sample_row.restype = C.c_int
+            self.lib.grpo_oracle_sample_row.argtypes = [_fp, C.c_int, C.c_double]
         else:
             self.lib.grpo_ref_last_error.restype = C.c_char_p
 
@@ -89,6 +93,16 @@ class _Lib:
         if self.kind == "port":
             raise RuntimeError(self.lib.grpo_oracle_strerror(rc).decode())
         raise RuntimeError(self.lib.grpo_ref_last_error().decode())
+
+    def row_logsumexp(self, row) -> float:
+        """apps/04_gpt2_grpo.cu:61-66 (port only; unpinned)."""
+        r = _as(row, _f)
+        return float(self.lib.grpo_oracle_row_logsumexp(r.ctypes.data_as(_fp), r.size))
+
+    def sample_row(self, row, coin: float) -> int:
+        """apps/04_gpt2_grpo.cu:68-80 with the uniform number given (port only; unpinned)."""
+        r = _as(row, _f)
+        return int(self.lib.grpo_oracle_sample_row(r.ctypes.data_as(_fp), r.size, float(coin)))
 
     def group_advantages(self, rewards, B, G, mode=STANDARDIZED, eps=1e-8):
         r = _as(rewards, _f)

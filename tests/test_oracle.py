@@ -285,3 +285,21 @@ def test_port_equals_reference_advantages():
     for mode in (0, 1):
         assert (bits(port.group_advantages(r, 12, 8, mode, 1e-8))
                 == bits(ref.group_advantages(r, 12, 8, mode, 1e-8))).all()
+
+
+def test_sampling_helpers_known_answers():
+    """row_logsumexp / sample_row (apps/04_gpt2_grpo.cu:61-80, unpinned restatement): uniform rows
+    have lse = x + log V and a coin u lands on floor(u * V); a one-hot-like row always returns its
+    peak; a coin past the accumulated mass falls back to V - 1."""
+    p = oracle_py.load("port")
+    x = np.full(1000, -2.25, np.float32)
+    assert abs(p.row_logsumexp(x) - (-2.25 + np.log(1000.0))) < 1e-12
+    for u in (0.0, 0.0005, 0.2503, 0.4996, 0.7307, 0.9985):  # away from the k/1000 boundaries
+        assert p.sample_row(x, u) == int(u * 1000)
+    peak = np.full(50, -40.0, np.float32)
+    peak[17] = 30.0
+    assert abs(p.row_logsumexp(peak) - 30.0) < 1e-12
+    assert all(p.sample_row(peak, u) == 17 for u in (1e-9, 0.5, 0.999999))
+    assert p.sample_row(peak, 1.0) == 49  # the cumulative sum never exceeds a coin of 1
+    two = np.array([np.log(0.25), np.log(0.75)], np.float32)
+    assert p.sample_row(two, 0.2499) == 0 and p.sample_row(two, 0.2501) == 1
