@@ -398,3 +398,37 @@ def test_row_order_partition_and_invariance():
             assert_grad(outs[1][0][:, :V], want[2], name)
     finally:
         D.set_variant(-1)
+
+
+@pytest.mark.parametrize("name,B,Gn,T,V,lengths", [
+    ("8x128x16", 1, 1, 3, 50257, [1]),           # fewer rows than clusters, one active row
+    ("8x128x16", 1, 2, 1, 40000, [1, 1]),        # one token per response
+    ("4x128x16", 2, 2, 40, 20000, [1, 40, 2, 39]),  # nearly empty next to full responses
+    ("1x128x16", 1, 3, 200, 777, [200, 1, 100]),    # many rows per cluster, several staging batches
+])
+def test_row_order_edge_shapes(name, B, Gn, T, V, lengths):
+    """The balanced row order on shapes at the edges of its index arithmetic: clusters without rows,
+    clusters with only masked or only active rows, more rows per cluster than one staging batch."""
+    import torch
+    from grpo_cpp_b200 import device as D
+    P = (V + 3) // 4 * 4
+    b = W.logits_case(B, Gn, T, V, sigma=2.0, min_len=1, reduction=W.SEQUENCE_MEAN, seed=V + T)
+    b.mask = W.prefix_mask(np.asarray(lengths), T).astype(np.int32)
+    b.selected = np.where(b.mask == 1, np.maximum(b.selected, 0), -1).astype(np.int32)
+    want = run_oracle(b)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    old, ref, sel, adv, mask = t(b.logp_old), t(b.logp_ref), t(b.selected), t(b.advantages), t(b.mask)
+    lens = D.count_lengths(mask, b.S, b.T)
+    weights, _ = D.weights_from_lengths(lens, b.reduction, 0.0)
+    try:
+        D.set_variant(D.variants().index(name))
+        x = t(b.padded(P))
+        assert D.plan(x, V) == name
+        res = D.logits(x, old, ref, sel, adv, weights, mask, b.T, V, b.clip_eps, b.beta, row_order=D.row_order(mask))
+        got = res.cpu().numpy()
+        assert (np.abs(got[:3] - want[0]) <= 1e-5 * np.abs(want[0]) + 1e-9).all() and got[3] == 0 and got[4] == 0
+        out = x.cpu().numpy()
+        assert_grad(out[:, :V], want[2], name)
+        assert (out[b.mask == 0] == 0).all() and (out[:, V:] == 0).all()
+    finally:
+        D.set_variant(-1)
