@@ -9,13 +9,14 @@ U[32,256], token-mean reduction with the global normaliser all-reduced), the con
 headline metric -- fused loss+dlogits tokens/s and HBM GB/s at 1/2/4/8 GPUs -- is quoted on.  The
 65,536 rows are split contiguously over the ranks (total work fixed: strong scaling).
 
-A step is one pass of the hot path over the batch: fused logits kernel in place (with the weights the
-previous pass left) -> per-row loss terms -> finalize; the mask's per-response lengths are counted
-for the next pass and travel with the result record in ONE all-reduce, after which the next
-pass's weights are derived.  The logits are restored from a pristine copy and L2 is flushed between
-passes on the same stream, outside the timed event pairs; the K passes are bracketed by a barrier
-and a synchronize, each is timed by a CUDA-event pair on the launching stream, and the per-rank
-totals are reduced with MAX.  One JSON line is printed by rank 0.
+A step is one pass of the hot path over the batch, two launches: the fused logits kernel in place (with
+the weights the previous pass left), then the reduce kernel (per-row loss terms in double, fixed-order
+totals, the next pass's per-response lengths, the exchange between the ranks through NVLink peer memory,
+the next pass's weights).  ``--exchange nccl`` runs the older form instead: lengths kernel, logits
+kernel, reduce kernel, ONE all-reduce, weights kernel.  The logits are restored from a pristine copy
+and L2 is flushed between passes on the same stream, outside the timed event pairs; the K passes are
+bracketed by a barrier and a synchronize, each is timed by a CUDA-event pair on the launching stream,
+and the per-rank totals are reduced with MAX.  One JSON line is printed by rank 0.
 
 ``--impl reference`` times the reference's own CPU implementation of the same path
 (oracle/_ref, the reference's src/cpu/grpo_loss.cpp compiled unmodified; the C restatement when

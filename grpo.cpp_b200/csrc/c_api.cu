@@ -1,5 +1,6 @@
-// Device layer of the C ABI: argument checks and kernel dispatch.  Nothing here allocates,
-// synchronises or exits; every pointer is a device pointer on the current device.
+// Device layer of the C ABI: argument checks and kernel dispatch.  The compute entry points neither
+// allocate nor synchronise nor exit, and every pointer they take is a device pointer on the current
+// device; only the exchange-region calls (create / export / open / close / destroy) manage memory.
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>

@@ -7,9 +7,11 @@
 //     8 B per fully masked group of the input streams is never fetched);
 //   * the three sums are carried in double from fp32 per-token products -- the same recipe as
 //     the CPU path (src/cpu/grpo_loss.cpp:114-116,157-159) -- through a fixed shuffle tree, a
-//     fixed warp-order tree per block and a fixed-order pass over per-block partials: no
-//     global atomics, bit-identical results from run to run;
-//   * no accumulator memset: the finalize step overwrites the result record.
+//     fixed warp-order tree per block and a fixed-order pass over per-block partials by the block
+//     that takes the last ticket: no floating-point atomics, bit-identical results from run to
+//     run, one kernel per pass;
+//   * no accumulator memset: the last block overwrites the result record (the only word cleared
+//     is the integer ticket counter, and not even that when the library owns the buffers).
 #include <mutex>
 
 #include "common.cuh"
@@ -19,7 +21,7 @@ namespace grpo_b200 {
 namespace {
 
 constexpr int kLossThreads = 256;
-constexpr int kLossMaxBlocks = 2048;  // bounds the per-block partials the finalize pass reads
+constexpr int kLossMaxBlocks = 2048;  // bounds the per-block partials the last block reads
 constexpr int kPartialWidth = 5;      // loss, pg, kl, bad gradients, bad inputs
 
 struct Acc {

@@ -1,12 +1,17 @@
 """Token-sharded execution of the logits path over ``torch.distributed`` (one process per GPU).
 
 The batch of ``N = S*T`` token rows is cut into contiguous row ranges, one per rank; a response
-may straddle two ranks.  Rows are independent given the per-response weight, so only two tiny
-exchanges exist, both plain sum all-reduces (NCCL over NVLink on GPUs):
+may straddle two ranks.  Rows are independent given the per-response weight, so the ranks only
+have to agree on two tiny things, both plain sums over ranks:
 
-1. before the kernel: the per-response valid-token counts (``int32[S]``), so that every rank
-   derives the same global lengths, the same token-count normaliser and the same weights;
-2. after the kernel: the result record (``float64[5]``: loss, pg, kl and the two error counts).
+1. the per-response valid-token counts (``S`` numbers), so that every rank derives the same
+   global lengths, the same token-count normaliser and the same weights;
+2. the result record (``float64[5]``: loss, pg, kl and the two error counts).
+
+Three ways to take the sums, by decreasing cost: :meth:`ShardedBoundary.step` (two all-reduces, no
+look-ahead), :meth:`~ShardedBoundary.step_fused` (one all-reduce per pass: the next pass's counts
+ride with this pass's record) and :meth:`~ShardedBoundary.step_peer` (no collective call: the
+pass's last kernel exchanges both through NVLink peer memory and also writes the next weights).
 
 ``dL/dlogits`` needs no communication.  The reference has no collective inside its loss path: its
 two-GPU demo shards whole responses under ``sequence_mean`` and divides by the device count on

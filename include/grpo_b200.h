@@ -70,7 +70,7 @@ enum { GRPO_B200_LOGITS_SEPARATE = 0, GRPO_B200_LOGITS_FUSED = 1 };
 /* reference include/grpo/grpo_loss.hpp:10-13 */
 enum { GRPO_B200_ADV_STANDARDIZED = 0, GRPO_B200_ADV_CENTERED = 1 };
 
-/* Device-side result record, written by the finalize step of each device call.
+/* Device-side result record, written by the last block of each device call's final kernel.
  * Sums are accumulated in double from fp32 per-token products, in a fixed order:
  * repeated runs on the same inputs give bit-identical records. */
 typedef struct {
