@@ -62,6 +62,33 @@ def shard_rows_balanced(mask, world: int, V: int, P: int, masked_cost: float = 0
     return [(cuts[r], cuts[r + 1] - cuts[r]) for r in range(world)]
 
 
+def global_group_advantages(local_rewards: torch.Tensor, n_prompts: int, local_G: int, *, mode: int = 0,
+                            eps: float = 1e-8, group=None, ops=None):
+    """Group-relative advantages when every rank rolled out ``local_G`` of each prompt's responses.
+
+    ``local_rewards`` is ``[n_prompts * local_G]`` (prompt-major).  The ranks all-gather their rewards,
+    lay them out as the global groups ``[prompt][source rank][g]`` -- the layout of the reference's
+    two-GPU GPT-2 demo (apps/05_two_gpu_gpt2_grpo.cu:168-202) -- compute the advantages of the whole
+    groups with the library's kernel (the reference does this step on the host), and return this
+    rank's slice ``[n_prompts * local_G]`` plus the count of non-finite values.  Everything stays on
+    the device; the one collective is the all-gather of ``n_prompts * local_G`` floats."""
+    if ops is None:
+        from . import device as ops  # the CUDA library; fails loudly when it is missing
+    if local_rewards.numel() != n_prompts * local_G:
+        raise RuntimeError(f"rewards has size {local_rewards.numel()}, expected {n_prompts * local_G}")
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    gathered = torch.empty(world, n_prompts, local_G, dtype=local_rewards.dtype, device=local_rewards.device)
+    if world > 1:
+        dist.all_gather_into_tensor(gathered.view(-1), local_rewards.contiguous().view(-1), group=group)
+    else:
+        gathered.view(-1).copy_(local_rewards.view(-1))
+    global_rewards = gathered.permute(1, 0, 2).contiguous().view(-1)  # [prompt][source][g]
+    adv, meta = ops.group_advantages(global_rewards, n_prompts, world * local_G, mode, eps)
+    mine = adv.view(n_prompts, world, local_G)[:, rank, :].contiguous().view(-1)
+    return mine, meta
+
+
 class ShardedBoundary:
     """One rank's view of the sharded loss boundary.
 

@@ -46,6 +46,12 @@ def weights_from_lengths(lengths, reduction, length_alpha=0.0, out=None, meta=No
     return out, meta
 
 
+def group_advantages(rewards, B, G, mode=0, eps=1e-8):
+    adv = oracle_py.load("port").group_advantages(rewards.numpy(), B, G, mode, eps)
+    bad = int((~np.isfinite(adv)).sum())
+    return torch.from_numpy(np.asarray(adv, np.float32)), torch.tensor([bad], dtype=torch.int32)
+
+
 def row_order(mask, out=None):
     m = mask.numpy() != 0
     idx = np.arange(m.size, dtype=np.int32)

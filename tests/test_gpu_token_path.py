@@ -184,3 +184,19 @@ def test_group_advantages_bit_exact():
         got, meta = D.group_advantages(torch.from_numpy(rewards).cuda(), B, Gn, mode, 1e-8)
         assert meta.item() == 0
         assert (got.cpu().numpy().view(np.uint32) == want.view(np.uint32)).all()
+
+
+@pytest.mark.gpu
+def test_global_group_advantages_single_rank_on_device():
+    """sharded.global_group_advantages without a process group (world 1): the device kernel on the
+    regrouped rewards, bit-exact against the oracle, all-equal groups exactly zero."""
+    import torch
+    from grpo_cpp_b200.sharded import global_group_advantages
+    rng = np.random.RandomState(9)
+    prompts, G_local = 7, 8
+    rewards = (rng.rand(prompts, G_local) < 0.4).astype(np.float32)
+    rewards[3] = 0.0
+    mine, meta = global_group_advantages(torch.from_numpy(rewards.reshape(-1)).cuda(), prompts, G_local)
+    want = oracle_py.load("best").group_advantages(rewards.reshape(-1), prompts, G_local)
+    assert (mine.cpu().numpy() == np.asarray(want)).all() and int(meta.cpu()[0]) == 0
+    assert (mine.cpu().numpy().reshape(prompts, G_local)[3] == 0).all()

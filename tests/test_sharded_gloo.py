@@ -148,3 +148,48 @@ def test_balanced_shards_cover_and_balance():
             work = [cost[o:o + c].sum() for o, c in spans]
             assert max(work) - min(work) <= 2 * (V + P)  # within a row or two of each other
     assert shard_rows_balanced(mask, 8, V, P) == shard_rows_balanced(mask, 8, V, P, 0.8)
+
+
+def _adv_worker(rank, world, port, queue):
+    try:
+        for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
+            sys.path.insert(0, p)
+        import cpu_ops
+        import oracle_py
+        import grpo_cpp_b200  # noqa: F401
+        from grpo_cpp_b200.sharded import global_group_advantages
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        prompts, local_G = 5, 3
+        rng = np.random.RandomState(4)
+        rewards = (rng.rand(world, prompts, local_G) < 0.5).astype(np.float32)  # [source][prompt][g]
+        rewards[:, 2, :] = 1.0  # an all-equal group: advantages exactly zero
+        mine, meta = global_group_advantages(torch.from_numpy(rewards[rank].reshape(-1).copy()), prompts, local_G,
+                                             ops=cpu_ops)
+        global_rewards = rewards.transpose(1, 0, 2).reshape(-1)  # [prompt][source][g], apps/05 layout
+        want = oracle_py.load("port").group_advantages(global_rewards, prompts, world * local_G)
+        want = np.asarray(want).reshape(prompts, world, local_G)[:, rank, :].reshape(-1)
+        assert (mine.numpy() == want).all() and int(meta[0]) == 0
+        assert (mine.numpy().reshape(prompts, local_G)[2] == 0).all()
+        queue.put((rank, "ok"))
+    except Exception:
+        queue.put((rank, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_global_group_advantages_over_gloo():
+    """Rewards all-gathered over two ranks, regrouped as the reference's two-GPU demo does, advantages
+    of the whole groups, this rank's slice back: equal to the oracle on the global batch."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_adv_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [queue.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
