@@ -444,7 +444,8 @@ def gpu_arm(args, spec: dict) -> None:
             "e2e": {"value": N * args.steps / e2e_total, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 48, "ms_per_step": 1e3 * e2e_total / args.steps,
                     "api": "grpo_logits_cuda_device_inplace (host metadata, device logits)" if world == 1 else
-                           "ShardedBoundary.prepare+step+stats from pinned host metadata"},
+                           ("ShardedBoundary.prepare+step_peer+stats from pinned host metadata (no collective call)"
+                            if peer else "ShardedBoundary.prepare+step+stats from pinned host metadata")},
             # per pass and rank: the row kernel and the reduce kernel (+ lengths and weights kernels with NCCL)
             "gpu_launches": (2 if peer else 4) * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

@@ -51,6 +51,8 @@ SIGNATURES = {
     "grpo_b200_logits_sharded": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _flt,
                                         _flt, _int, _int, _vp, _vp, _vp, _vp, _sz, C.POINTER(_vp), _int, _int, _i64,
                                         _vp, _int, _flt, _vp, _vp, _vp, _vp]),
+    "grpo_b200_lengths_sharded": (_int, [_vp, _i64, _i64, _int, _i64, C.POINTER(_vp), _int, _int, _int, _flt, _vp, _vp,
+                                         _vp, _vp, _sz, _vp]),
     "grpo_b200_sample_rows": (_int, [_vp, _i64, _int, _int, _vp, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "grpo_b200_logits_set_variant": (_int, [_int]),
     "grpo_b200_logits_variant_name": (C.c_char_p, [_int]),

@@ -353,6 +353,56 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                        workspace, workspace_bytes, x, stream);
 }
 
+int grpo_b200_lengths_sharded(const int32_t* mask, int64_t n_rows, int64_t row_offset, int tokens_per_seq,
+                              int64_t n_seq, void* const* regions, int rank, int world, int reduction,
+                              float length_alpha, float* weights, int32_t* meta, double* lengths, void* workspace,
+                              size_t workspace_bytes, grpo_b200_stream_t stream) {
+    if (world < 1 || world > kExchangeMaxWorld) return invalid("world must lie in [1, 8]");
+    if (rank < 0 || rank >= world) return invalid("rank must lie in [0, world)");
+    if (!mask || !regions || !weights || !meta || n_seq <= 0)
+        return invalid("mask, regions, weights and meta must not be null and n_seq must be positive");
+    if (n_rows <= 0 || tokens_per_seq <= 0 || row_offset < 0) return invalid("B, G and T must be positive");
+    if (row_offset + n_rows > kIntMax) return invalid("token count exceeds INT_MAX");
+    if ((row_offset + n_rows + tokens_per_seq - 1) / tokens_per_seq > n_seq)
+        return invalid("rows reach beyond the last response");
+    if (reduction < GRPO_B200_SEQUENCE_MEAN || reduction > GRPO_B200_LENGTH_WEIGHTED)
+        return invalid("unknown reduction mode");
+    if (!workspace || workspace_bytes < grpo_b200_logits_workspace_bytes(n_rows) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 31u)) {
+        set_error("workspace must be 32-byte aligned and hold grpo_b200_logits_workspace_bytes() bytes");
+        return GRPO_B200_E_WORKSPACE;
+    }
+    ExchangeArgs x = {};
+    for (int r = 0; r < world; r++) {
+        if (!regions[r]) return invalid("every rank's exchange region must be mapped");
+        x.peers[r] = static_cast<unsigned char*>(regions[r]);
+    }
+    x.rank = rank;
+    x.world = world;
+    x.n_seq = n_seq;
+    x.next_mask = mask;
+    x.reduction = reduction;
+    x.length_alpha = length_alpha;
+    x.weights_out = weights;
+    x.meta_out = meta;
+    x.lengths_out = lengths;
+    // the reduce kernel with no rows to reduce: it counts, exchanges (an all-zero record rides along) and
+    // derives the weights; the record lands in the unused row area of the workspace
+    LogitsArgs a = {};
+    a.n_rows = n_rows;
+    a.row_offset = row_offset;
+    a.tokens_per_seq = tokens_per_seq;
+    a.rows = static_cast<RowRecord*>(workspace);
+    a.result = static_cast<grpo_b200_result_t*>(workspace);
+    a.status = reinterpret_cast<int*>(a.rows + n_rows);
+    a.counter = reinterpret_cast<unsigned*>(a.status) + 1;
+    a.partials = reinterpret_cast<double*>(reinterpret_cast<unsigned char*>(a.status) + 32);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    GRPO_CUDA_TRY(cudaMemsetAsync(a.status, 0, 32, s));
+    GRPO_CUDA_TRY(launch_logits_reduce(a, x, s));
+    return GRPO_B200_OK;
+}
+
 int grpo_b200_sample_rows(const float* logits, int64_t n_rows, int V, int P, const int32_t* rows, int n_selected,
                           const double* coins, const int32_t* given_tokens, int32_t* tokens_out, float* logp_out,
                           double* lse_out, grpo_b200_stream_t stream) {

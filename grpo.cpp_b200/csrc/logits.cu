@@ -940,7 +940,8 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
     // Everything above and the loads just below depend on nothing the row kernel writes: they may run
     // while its last CTAs are still working (programmatic dependent launch).  From here on its
     // records, status word and cleared ticket counter are needed.
-    const bool row_active = row < a.n_rows && a.mask[row] != 0;
+    // (a null mask: a lengths-only exchange, launched on its own with no rows to reduce)
+    const bool row_active = a.mask != nullptr && row < a.n_rows && a.mask[row] != 0;
     RowScalars sc = {0.0f, 0.0f, 0.0f, 0.0f};
     if (row_active) sc = load_row_scalars(a, row);
     asm volatile("griddepcontrol.wait;" ::: "memory");

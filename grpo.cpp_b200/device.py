@@ -264,6 +264,22 @@ def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advanta
     return result
 
 
+def lengths_sharded(mask: torch.Tensor, n_seq: int, tokens_per_seq: int, row_offset: int, *, exchange: PeerExchange,
+                    reduction: int, length_alpha: float, weights: torch.Tensor, meta: torch.Tensor,
+                    workspace: torch.Tensor, lengths: torch.Tensor | None = None) -> torch.Tensor:
+    """Global per-response lengths of ``mask`` (this rank's rows) summed over the ranks through their
+    exchange regions, and the weights derived from them: what the first pass needs, without a
+    collective call.  Counts as one pass of the region."""
+    exchange.passes += 1
+    _lib.check(_lib.lib().grpo_b200_lengths_sharded(
+        _check_tensor(mask, torch.int32, "mask"), mask.numel(), row_offset, tokens_per_seq, n_seq, exchange.regions,
+        exchange.rank, exchange.world, int(reduction), float(length_alpha),
+        _check_tensor(weights, torch.float32, "weights"), _check_tensor(meta, torch.int32, "meta"),
+        None if lengths is None else _check_tensor(lengths, torch.float64, "lengths"),
+        workspace.data_ptr(), workspace.numel(), _stream()))
+    return weights
+
+
 def sample_rows(logits_t: torch.Tensor, V: int, rows: torch.Tensor, *, coins: torch.Tensor | None = None,
                 tokens: torch.Tensor | None = None):
     """For the rows of ``logits_t`` (``[n_rows, P]`` fp32) named in ``rows`` (int32): the row

@@ -132,9 +132,14 @@ class ShardedBoundary:
         """Exchange 1: global lengths and weights from this rank's slice of the mask."""
         if mask_local.numel() != self.n_local:
             raise RuntimeError(f"mask has size {mask_local.numel()}, expected {self.n_local}")
-        self.ops.count_lengths(mask_local, self.S, self.T, self.row_offset, self.lengths)
-        self._all_reduce(self.lengths)
-        self.ops.weights_from_lengths(self.lengths, self.reduction, self.alpha, self.weights, self.meta)
+        if self.exchange is not None:  # through the ranks' regions: no collective call
+            self.ops.lengths_sharded(mask_local, self.S, self.T, self.row_offset, exchange=self.exchange,
+                                     reduction=self.reduction, length_alpha=self.alpha, weights=self.weights,
+                                     meta=self.meta, workspace=self.workspace, lengths=self.lengths_f64)
+        else:
+            self.ops.count_lengths(mask_local, self.S, self.T, self.row_offset, self.lengths)
+            self._all_reduce(self.lengths)
+            self.ops.weights_from_lengths(self.lengths, self.reduction, self.alpha, self.weights, self.meta)
         self.row_order = self.ops.row_order(mask_local, self.row_order)
 
     def step(self, logits_local, logp_old, logp_ref, selected, advantages, mask_local,

@@ -241,6 +241,19 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
                              float length_alpha, float* next_weights, int32_t* next_meta,
                              double* next_lengths, grpo_b200_stream_t stream);
 
+/* The first pass's weights without a collective call: counts mask's valid tokens per response
+ * among this rank's rows, sums the counts over the ranks through their exchange regions (the
+ * exchange of grpo_b200_logits_sharded, with an all-zero record) and derives the weights.
+ * Replaces make_weights (src/cuda/grpo_loss_cuda.cu:21-57) for a batch whose rows are spread
+ * over ranks.  weights[n_seq], meta[2] and lengths[n_seq] (nullable) as in
+ * grpo_b200_logits_sharded; workspace as for grpo_b200_logits on n_rows rows.  Counts as one
+ * pass of the region: every rank makes the call. */
+int grpo_b200_lengths_sharded(const int32_t* mask, int64_t n_rows, int64_t row_offset,
+                              int tokens_per_seq, int64_t n_seq, void* const* regions, int rank,
+                              int world, int reduction, float length_alpha, float* weights,
+                              int32_t* meta, double* lengths, void* workspace,
+                              size_t workspace_bytes, grpo_b200_stream_t stream);
+
 /* Sampling and log-probability extraction on logits that stay on the device.  Replaces, for
  * the rows named in rows[n_selected] (indices into the [n_rows][P] logits), the host-side
  * row_logsumexp / sample_row / draw_sample of apps/04_gpt2_grpo.cu:61-80,138-161, which need

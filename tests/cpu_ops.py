@@ -124,3 +124,17 @@ def logits_sharded(logits_t, logp_old, logp_ref, selected, advantages, weights, 
         next_lengths.copy_(counts)
     weights_from_lengths(counts.to(torch.int32), reduction, length_alpha, next_weights, next_meta)
     return result
+
+
+def lengths_sharded(mask, n_seq, tokens_per_seq, row_offset, *, exchange, reduction, length_alpha, weights, meta,
+                    workspace, lengths=None):
+    import torch.distributed as dist
+    assert exchange.peers is not None, "regions must be mapped before the first pass"
+    exchange.passes += 1
+    counts = count_lengths(mask, n_seq, tokens_per_seq, row_offset).to(torch.float64)
+    if exchange.world > 1:
+        dist.all_reduce(counts)
+    if lengths is not None:
+        lengths.copy_(counts)
+    weights_from_lengths(counts.to(torch.int32), reduction, length_alpha, weights, meta)
+    return weights

@@ -349,7 +349,10 @@ def test_peer_exchange_pass_single_rank():
                          length_alpha=b.length_alpha, device=torch.device("cuda"))
     old, ref, sel, adv, mask = t(b.logp_old), t(b.logp_ref), t(b.selected), t(b.advantages), t(b.mask)
     sb.prepare(mask)
+    first = sb.weights.clone()
     sb.enable_peer_exchange()
+    sb.prepare(mask)  # now through the exchange region (grpo_b200_lengths_sharded): the same weights, bit for bit
+    assert (sb.weights == first).all() and sb.meta.cpu().tolist() == [int(b.mask.sum()), 0]
     try:
         for _ in range(3):
             x = t(b.padded(P))

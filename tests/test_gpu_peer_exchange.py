@@ -45,7 +45,11 @@ def _worker(rank, world, port, reduction, alpha, queue):
         sb.prepare(mask)  # the first pass's weights: one collective call, before the exchange exists
         want = oracle_py.load("port").logits(b.logits, b.logp_old, b.logp_ref, b.selected, b.advantages, b.mask,
                                              b.B, b.G, b.T, b.V, **b.cfg())
+        first = sb.weights.clone()
         sb.enable_peer_exchange()
+        sb.prepare(mask)  # again, by the library's own exchange: the same global lengths and weights
+        assert (sb.weights == first).all()
+        assert sb.lengths_f64.cpu().numpy().astype(np.int64).tolist() == b.mask.reshape(b.S, b.T).sum(1).tolist()
         for _ in range(3):
             x = t(b.padded(P)[sl])
             sb.step_peer(x, old, ref, sel, adv, mask)

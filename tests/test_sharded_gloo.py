@@ -60,11 +60,12 @@ def _worker(rank, world, port, case, queue):
         if peer:
             # as below, through the path whose exchange the last kernel of the pass does itself
             sb.enable_peer_exchange()
+            sb.prepare(t(b.mask[sl]))  # again, now through the exchange: the same weights
             scratch = x.clone()
             sb.step_peer(scratch, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages),
                          t(b.mask[sl]))
             sb.step_peer(x, t(b.logp_old[sl]), t(b.logp_ref[sl]), t(b.selected[sl]), t(b.advantages), t(b.mask[sl]))
-            assert sb.exchange.passes == 2
+            assert sb.exchange.passes == 3
         elif fused:
             # two passes over the batch with one collective each: the second pass runs on the weights
             # that rode along with the first pass's result record
