@@ -98,3 +98,19 @@ def test_sampling_avoids_the_host_copy():
     print(f"\nsample {S} of {N} rows on the device: {t_dev * 1e3:.3f} ms; copying the {N * P * 4 / 1e6:.0f} MB of "
           f"logits to pinned host memory alone: {t_copy * 1e3:.1f} ms")
     assert t_dev < t_copy
+
+
+def test_sampling_against_committed_vectors():
+    import torch
+    from conftest import Golden
+    from grpo_cpp_b200 import device as D
+    g = Golden("sampling_cases.npz")
+    for name in g.cases:
+        c = g.case(name)
+        x = np.ascontiguousarray(c["logits"])
+        n, V = x.shape
+        tok, logp, lse = D.sample_rows(torch.from_numpy(x).cuda(), V, torch.arange(n, dtype=torch.int32, device="cuda"),
+                                       coins=torch.from_numpy(c["coins"]).cuda())
+        assert (tok.cpu().numpy() == c["tokens"]).all()
+        assert np.abs(lse.cpu().numpy() - c["lse"]).max() <= 1e-12 * np.maximum(1.0, np.abs(c["lse"])).max()
+        assert np.abs(logp.cpu().numpy() - c["logp"]).max() <= 1e-6

@@ -303,3 +303,15 @@ def test_sampling_helpers_known_answers():
     assert p.sample_row(peak, 1.0) == 49  # the cumulative sum never exceeds a coin of 1
     two = np.array([np.log(0.25), np.log(0.75)], np.float32)
     assert p.sample_row(two, 0.2499) == 0 and p.sample_row(two, 0.2501) == 1
+
+
+def test_sampling_helpers_against_committed_vectors():
+    """tests/golden/sampling_cases.npz freezes the restatement of apps/04_gpt2_grpo.cu:61-80."""
+    from conftest import Golden
+    g = Golden("sampling_cases.npz")
+    p = oracle_py.load("port")
+    for name in g.cases:
+        c = g.case(name)
+        for i in range(len(c["coins"])):
+            assert p.row_logsumexp(c["logits"][i]) == c["lse"][i]
+            assert p.sample_row(c["logits"][i], c["coins"][i]) == c["tokens"][i]
