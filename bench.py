@@ -485,6 +485,9 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gpt2", choices=["gpt2", "gpt2s", "v32k", "v128k"])
     ap.add_argument("--variant", type=int, default=None, help="force a row-resident kernel variant")
+    ap.add_argument("--prompts", type=int, default=None,
+                    help="override the workload's number of prompts B (rows = B x G x T): the same row shape at "
+                         "another batch size, e.g. to see the kernel's steady-state rate on a short configuration")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="at more than one rank: the pass's exchange by the library's own kernel over NVLink peer "
@@ -495,6 +498,9 @@ def main() -> None:
     args = ap.parse_args()
     import grpo_cpp_b200  # noqa: F401  (registers the package under its importable name)
     spec = workload_spec(args.workload)
+    if args.prompts is not None:
+        spec["B"] = args.prompts
+        spec["label"] += f" (B overridden to {args.prompts})"
     if args.impl == "reference":
         reference_arm(args, spec)
     else:
