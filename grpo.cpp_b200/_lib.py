@@ -52,11 +52,13 @@ SIGNATURES = {
                                         _flt, _int, _int, _vp, _vp, _vp, _vp, _sz, C.POINTER(_vp), _int, _int, _i64,
                                         _vp, _int, _flt, _vp, _vp, _vp, _vp]),
     "grpo_b200_lengths_sharded": (_int, [_vp, _i64, _i64, _int, _i64, C.POINTER(_vp), _int, _int, _int, _flt, _vp, _vp,
-                                         _vp, _vp, _sz, _vp]),
+                                         _vp, _vp, _vp, _sz, _vp]),
+    "grpo_b200_exchange_set_timeout_cycles": (_int, [_i64]),
+    "grpo_b200_synthetic_logits": (_int, [_vp, _i64, _i64, _int, _int, _flt, C.c_uint64, _flt, _vp]),
     "grpo_b200_sample_rows": (_int, [_vp, _i64, _int, _int, _vp, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "grpo_b200_logits_set_variant": (_int, [_int]),
     "grpo_b200_logits_variant_name": (C.c_char_p, [_int]),
-    "grpo_b200_logits_plan": (C.c_char_p, [_vp, _vp, _int, _int, _int]),
+    "grpo_b200_logits_plan": (C.c_char_p, [_vp, _vp, _int, _int, _i64, _int]),
     "grpo_b200_loss_host": (_int, [_f, _sz, _f, _sz, _f, _sz, _f, _sz, _i, _sz, _int, _int, _int, _flt, _flt, _int,
                                    _flt, _int, _f, _f, C.POINTER(_int)]),
     "grpo_b200_logits_host": (_int, [_f, _sz, _f, _sz, _f, _sz, _i, _sz, _f, _sz, _i, _sz, _int, _int, _int, _int,

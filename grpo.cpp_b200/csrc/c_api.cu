@@ -4,7 +4,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -46,6 +49,24 @@ int check_options(float clip_eps, float beta) {
 }
 
 constexpr long long kIntMax = 2147483647LL;
+
+// Exchange regions created by this process, with the response count each was sized for: a sharded
+// call whose n_seq differs from its own region's would write past the end of every rank's region.
+std::mutex g_regions_mutex;
+std::unordered_map<const void*, long long> g_regions;
+std::atomic<long long> g_exchange_timeout_cycles{kDefaultExchangeTimeoutCycles};
+
+// 0: the own region is unknown to this process (mapped from elsewhere) or matches; else an error code
+int check_own_region(void* const* regions, int rank, int64_t n_seq) {
+    std::lock_guard<std::mutex> lock(g_regions_mutex);
+    auto it = g_regions.find(regions[rank]);
+    if (it != g_regions.end() && it->second != n_seq) {
+        set_error("n_seq is %lld but this rank's exchange region was created for %lld responses",
+                  static_cast<long long>(n_seq), it->second);
+        return GRPO_B200_E_INVALID;
+    }
+    return GRPO_B200_OK;
+}
 
 }  // namespace
 
@@ -229,7 +250,7 @@ int logits_pass(const float* logits, float* dlogits, const float* logp_old, cons
     a.counter = reinterpret_cast<unsigned*>(a.status) + 1;
     a.partials = reinterpret_cast<double*>(reinterpret_cast<unsigned char*>(a.status) + 32);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    const int variant = kernel == GRPO_B200_LOGITS_FUSED ? pick_resident_variant(logits, dlogits, V, P) : -1;
+    const int variant = kernel == GRPO_B200_LOGITS_FUSED ? pick_resident_variant(logits, dlogits, V, P, n_rows) : -1;
     if (variant >= 0)
         GRPO_CUDA_TRY(launch_logits_resident(variant, check_inputs != 0, a, s));
     else
@@ -282,7 +303,17 @@ int grpo_b200_exchange_create(int64_t n_seq, void** region) {
         cudaFree(p);
         return cuda_fail(err, "clearing the exchange region");
     }
+    {
+        std::lock_guard<std::mutex> lock(g_regions_mutex);
+        g_regions[p] = n_seq;
+    }
     *region = p;
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_exchange_set_timeout_cycles(int64_t cycles) {
+    if (cycles <= 0) return invalid("the exchange timeout must be a positive number of SM clock cycles");
+    g_exchange_timeout_cycles.store(cycles, std::memory_order_relaxed);
     return GRPO_B200_OK;
 }
 
@@ -313,6 +344,10 @@ int grpo_b200_exchange_close(void* peer_region) {
 
 int grpo_b200_exchange_destroy(void* region) {
     if (!region) return GRPO_B200_OK;
+    {
+        std::lock_guard<std::mutex> lock(g_regions_mutex);
+        g_regions.erase(region);
+    }
     GRPO_CUDA_TRY(cudaFree(region));
     return GRPO_B200_OK;
 }
@@ -331,6 +366,7 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
         return invalid("regions, next_mask, next_weights and next_meta must not be null and n_seq must be positive");
     if (reduction < GRPO_B200_SEQUENCE_MEAN || reduction > GRPO_B200_LENGTH_WEIGHTED)
         return invalid("unknown reduction mode");
+    if (!(length_alpha >= 0.0f && length_alpha <= 1.0f)) return invalid("length_alpha must be finite and in [0, 1]");
     if (tokens_per_seq > 0 && n_rows > 0 && row_offset >= 0 &&
         (row_offset + n_rows + tokens_per_seq - 1) / tokens_per_seq > n_seq)
         return invalid("rows reach beyond the last response");
@@ -339,6 +375,8 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
         if (!regions[r]) return invalid("every rank's exchange region must be mapped");
         x.peers[r] = static_cast<unsigned char*>(regions[r]);
     }
+    if (int rc = check_own_region(regions, rank, n_seq)) return rc;
+    x.timeout_cycles = g_exchange_timeout_cycles.load(std::memory_order_relaxed);
     x.rank = rank;
     x.world = world;
     x.n_seq = n_seq;
@@ -355,18 +393,20 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
 
 int grpo_b200_lengths_sharded(const int32_t* mask, int64_t n_rows, int64_t row_offset, int tokens_per_seq,
                               int64_t n_seq, void* const* regions, int rank, int world, int reduction,
-                              float length_alpha, float* weights, int32_t* meta, double* lengths, void* workspace,
-                              size_t workspace_bytes, grpo_b200_stream_t stream) {
+                              float length_alpha, float* weights, int32_t* meta, double* lengths,
+                              grpo_b200_result_t* status, void* workspace, size_t workspace_bytes,
+                              grpo_b200_stream_t stream) {
     if (world < 1 || world > kExchangeMaxWorld) return invalid("world must lie in [1, 8]");
     if (rank < 0 || rank >= world) return invalid("rank must lie in [0, world)");
-    if (!mask || !regions || !weights || !meta || n_seq <= 0)
-        return invalid("mask, regions, weights and meta must not be null and n_seq must be positive");
+    if (!mask || !regions || !weights || !meta || !status || n_seq <= 0)
+        return invalid("mask, regions, weights, meta and status must not be null and n_seq must be positive");
     if (n_rows <= 0 || tokens_per_seq <= 0 || row_offset < 0) return invalid("B, G and T must be positive");
     if (row_offset + n_rows > kIntMax) return invalid("token count exceeds INT_MAX");
     if ((row_offset + n_rows + tokens_per_seq - 1) / tokens_per_seq > n_seq)
         return invalid("rows reach beyond the last response");
     if (reduction < GRPO_B200_SEQUENCE_MEAN || reduction > GRPO_B200_LENGTH_WEIGHTED)
         return invalid("unknown reduction mode");
+    if (!(length_alpha >= 0.0f && length_alpha <= 1.0f)) return invalid("length_alpha must be finite and in [0, 1]");
     if (!workspace || workspace_bytes < grpo_b200_logits_workspace_bytes(n_rows) ||
         (reinterpret_cast<uintptr_t>(workspace) & 31u)) {
         set_error("workspace must be 32-byte aligned and hold grpo_b200_logits_workspace_bytes() bytes");
@@ -377,6 +417,8 @@ int grpo_b200_lengths_sharded(const int32_t* mask, int64_t n_rows, int64_t row_o
         if (!regions[r]) return invalid("every rank's exchange region must be mapped");
         x.peers[r] = static_cast<unsigned char*>(regions[r]);
     }
+    if (int rc = check_own_region(regions, rank, n_seq)) return rc;
+    x.timeout_cycles = g_exchange_timeout_cycles.load(std::memory_order_relaxed);
     x.rank = rank;
     x.world = world;
     x.n_seq = n_seq;
@@ -387,13 +429,13 @@ int grpo_b200_lengths_sharded(const int32_t* mask, int64_t n_rows, int64_t row_o
     x.meta_out = meta;
     x.lengths_out = lengths;
     // the reduce kernel with no rows to reduce: it counts, exchanges (an all-zero record rides along) and
-    // derives the weights; the record lands in the unused row area of the workspace
+    // derives the weights; the exchanged record (bad_inputs = -2 when a rank did not answer) goes to `status`
     LogitsArgs a = {};
     a.n_rows = n_rows;
     a.row_offset = row_offset;
     a.tokens_per_seq = tokens_per_seq;
     a.rows = static_cast<RowRecord*>(workspace);
-    a.result = static_cast<grpo_b200_result_t*>(workspace);
+    a.result = status;
     a.status = reinterpret_cast<int*>(a.rows + n_rows);
     a.counter = reinterpret_cast<unsigned*>(a.status) + 1;
     a.partials = reinterpret_cast<double*>(reinterpret_cast<unsigned char*>(a.status) + 32);
@@ -419,16 +461,26 @@ int grpo_b200_sample_rows(const float* logits, int64_t n_rows, int V, int P, con
 }
 
 int grpo_b200_logits_set_variant(int variant) {
-    if (variant >= resident_variant_count()) return invalid("no such kernel variant");
-    g_forced_variant = variant < 0 ? -1 : variant;
+    if (set_forced_variant(variant) != 0) return invalid("no such kernel variant");
+    return GRPO_B200_OK;
+}
+
+int grpo_b200_synthetic_logits(float* logits, int64_t n_rows, int64_t row_offset, int V, int P, float scale,
+                               uint64_t seed, float tail_fill, grpo_b200_stream_t stream) {
+    if (!logits) return invalid("device pointers must not be null");
+    if (n_rows <= 0 || row_offset < 0 || row_offset + n_rows > kIntMax) return invalid("n_rows must lie in [1, INT_MAX]");
+    if (V <= 0) return invalid("V must be positive");
+    if (P < V) return invalid("P must be at least V");
+    GRPO_CUDA_TRY(launch_synthetic_logits(logits, n_rows, row_offset, V, P, scale, seed, tail_fill,
+                                          reinterpret_cast<cudaStream_t>(stream)));
     return GRPO_B200_OK;
 }
 
 const char* grpo_b200_logits_variant_name(int variant) { return resident_variant_name(variant); }
 
-const char* grpo_b200_logits_plan(const void* logits, const void* dlogits, int V, int P, int kernel) {
+const char* grpo_b200_logits_plan(const void* logits, const void* dlogits, int V, int P, int64_t n_rows, int kernel) {
     if (kernel != GRPO_B200_LOGITS_FUSED) return "streaming";
-    const int v = pick_resident_variant(logits, dlogits, V, P);
+    const int v = pick_resident_variant(logits, dlogits, V, P, n_rows);
     return v >= 0 ? resident_variant_name(v) : "streaming";
 }
 

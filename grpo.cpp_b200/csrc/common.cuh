@@ -212,7 +212,7 @@ struct LogitsArgs {
     RowRecord* rows;    // [n_rows] per-row hand-over between the row kernel and the reduce kernel
     float* selected_logp;
     grpo_b200_result_t* result;
-    int* status;        // set non-zero when a bounded pipeline wait gave up
+    int* status;        // bit 0: a bounded pipeline wait gave up; bit 1: row_order does not match the mask
     unsigned* counter;  // ticket counter of the reduce kernel's blocks (zeroed with the status word)
     double* partials;   // [ceil(n_rows / 256)][5] per-block sums of the reduce kernel
 };
@@ -245,15 +245,23 @@ struct ExchangeArgs {
     float* weights_out;  // [n_seq] the next pass's weights
     int32_t* meta_out;   // {valid tokens, empty responses} of the next pass's mask
     double* lengths_out; // [n_seq] global valid-token counts of the next pass's mask (nullable)
+    long long timeout_cycles;  // SM clock cycles the exchange poll may wait for the peers before it gives up
 };
+constexpr long long kDefaultExchangeTimeoutCycles = 1LL << 32;  // about two seconds
+// status word of a pass and the negative bad_inputs values the reduce kernel derives from it
+constexpr int kStatusPipelineTimeout = 1;
+constexpr int kStatusRowOrderMismatch = 2;
+constexpr double kBadInputsPipelineTimeout = -1.0;
+constexpr double kBadInputsExchangeTimeout = -2.0;
+constexpr double kBadInputsRowOrder = -3.0;
 // flags stored in row_terms.w (small integers, exact in fp32)
 constexpr float kRowBadGrad = 1.0f;
 constexpr float kRowBadInput = 2.0f;
 
-int pick_resident_variant(const void* logits, const void* dlogits, int V, int P);
+int pick_resident_variant(const void* logits, const void* dlogits, int V, int P, long long n_rows);
+int set_forced_variant(int variant);
 const char* resident_variant_name(int variant);
 int resident_variant_count();
-extern int g_forced_variant;
 cudaError_t launch_logits_resident(int variant, bool check, const LogitsArgs& a, cudaStream_t stream);
 cudaError_t launch_logits_streaming(bool check, const LogitsArgs& a, cudaStream_t stream);
 cudaError_t launch_logits_reduce(const LogitsArgs& a, const ExchangeArgs& x, cudaStream_t stream);
@@ -270,6 +278,8 @@ cudaError_t launch_weights_f64(const double* lengths, long long n_seq, int reduc
 cudaError_t launch_sample_rows(const float* logits, long long n_rows, int V, int P, const int32_t* rows, int n_sel,
                                const double* coins, const int32_t* given, int32_t* tokens_out, float* logp_out,
                                double* lse_out, cudaStream_t stream);
+cudaError_t launch_synthetic_logits(float* out, long long n_rows, long long row_offset, int V, int P, float scale,
+                                    unsigned long long seed, float tail_fill, cudaStream_t stream);
 cudaError_t launch_row_order(const int32_t* mask, long long n_rows, int32_t* order, cudaStream_t stream);
 cudaError_t launch_group_advantages(const float* rewards, int B, int G, int mode, float eps,
                                     float* advantages, int32_t* meta, cudaStream_t stream);

@@ -223,8 +223,13 @@ int check_selected(const int32_t* selected, const int32_t* mask, size_t n, int V
 }
 
 int fill_stats(const grpo_b200_result_t& r, float* stats, const char* what) {
-    if (r.bad_inputs < 0.0) {  // the kernel's bounded pipeline wait gave up
-        set_error("CUDA error: logits kernel abandoned a stalled copy pipeline");
+    if (r.bad_inputs < 0.0) {  // the pass itself failed (include/grpo_b200.h, grpo_b200_result_t)
+        if (r.bad_inputs == kBadInputsRowOrder)
+            set_error("CUDA error: the row order handed to the logits kernel does not belong to the mask");
+        else if (r.bad_inputs == kBadInputsExchangeTimeout)
+            set_error("CUDA error: the exchange between ranks timed out");
+        else
+            set_error("CUDA error: logits kernel abandoned a stalled copy pipeline");
         return GRPO_B200_E_CUDA;
     }
     stats[0] = static_cast<float>(r.loss);

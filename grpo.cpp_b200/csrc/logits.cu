@@ -46,28 +46,13 @@
 // columns of a masked row and over columns [V, P) of an active one.
 #include <cooperative_groups.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace grpo_b200 {
-
-int g_forced_variant = -1;
-
-// Build-time diagnostic (-DGRPO_TIMELINE): CTA 0 records the SM clock at the phase boundaries of
-// sixteen of its active rows, for threads 0 and THREADS-1, into a device array that a debug call copies out.
-#ifdef GRPO_TIMELINE
-__device__ long long g_timeline[2][16][8];
-__device__ int g_timeline_grid;
-#define GRPO_TL(phase)                                                                          \
-    do {                                                                                        \
-        if (blockIdx.x == 0 && (tid == 0 || tid == THREADS - 1) && tl_row >= 0 && tl_row < 16)  \
-            g_timeline[tid == 0 ? 0 : 1][tl_row][phase] = clock64();                            \
-        if ((phase) == 7) tl_row++;                                                             \
-    } while (0)
-#else
-#define GRPO_TL(phase) do { } while (0)
-#endif
 
 namespace {
 
@@ -405,7 +390,16 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     // clusters carry the same load to within a row, interleaved evenly (slot k is an active row
     // when floor((k+1) * mine_active / n_mine) steps up) so that zero fills keep overlapping with
     // the active rows' phases.
+    // A row order whose two counts do not add up to the row count belongs to another batch: it is
+    // ignored (every CTA reads the same two words, so the decision is uniform) and the pass reports it.
     const int* order = a.row_order;
+    if (order) {
+        const int na = order[0], nm = order[1];
+        if (na < 0 || nm < 0 || static_cast<long long>(na) + nm != a.n_rows) {
+            order = nullptr;
+            if (blockIdx.x == 0 && tid == 0) atomicOr(&abort_sh, kStatusRowOrderMismatch);
+        }
+    }
     const int total_active = order ? order[0] : 0;
     const int total_masked = order ? order[1] : 0;
     const int* active_rows = order ? order + 2 : nullptr;
@@ -419,13 +413,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     bool alive = true;  // false after a wait timed out: skip the ring, keep meeting barriers
     unsigned row_parity = 0;
     unsigned xuses[2] = {0u, 0u};
-#ifdef GRPO_TIMELINE
-#ifndef GRPO_TL_SKIP
-#define GRPO_TL_SKIP 0
-#endif
-    int tl_row = -(GRPO_TL_SKIP);  // active rows of CTA 0 to let pass before recording starts
-    if (blockIdx.x == 0 && threadIdx.x == 0) g_timeline_grid = static_cast<int>(gridDim.x);
-#endif
 
     if (is_producer) {
         // ---- producer warp: free-running over all of this cluster's rows.  The lanes read 32 rows'
@@ -441,7 +428,10 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                 const int k = base + lane;
                 if (k >= n_cand) return -1;
                 const size_t at = static_cast<size_t>(cluster_id) + static_cast<size_t>(k) * n_clusters;
-                if (order) return active_rows[at];
+                if (order) {
+                    const int r = active_rows[at];
+                    return r >= 0 && r < n_rows ? r : -1;  // a row index outside the batch is never loaded
+                }
                 return a.mask[at] != 0 ? static_cast<int>(at) : -1;
             };
             int next_row = group_rows(0);
@@ -461,7 +451,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                             const unsigned parity = (q / STAGES) & 1u;
                             if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
                                 alive = false;
-                                abort_sh = 1;
+                                atomicOr(&abort_sh, kStatusPipelineTimeout);
                                 break;
                             }
                             const int first = t * TILE_CHUNKS;
@@ -489,13 +479,23 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                 const long long before = k * mine_active / n_mine;  // active rows among this cluster's first k
                 mk = (k + 1) * mine_active / n_mine > before;
                 const size_t nth = mk ? static_cast<size_t>(before) : static_cast<size_t>(k - before);
-                r = static_cast<size_t>((mk ? active_rows : masked_rows)[static_cast<size_t>(cluster_id) + nth * n_clusters]);
+                const int listed = (mk ? active_rows : masked_rows)[static_cast<size_t>(cluster_id) + nth * n_clusters];
+                // the list must name rows of this batch and agree with the mask the reduce kernel reads;
+                // a row it misplaces is skipped (nothing loaded, nothing stored) and the pass reports it
+                if (listed < 0 || listed >= n_rows) {
+                    mk = 2;
+                    r = 0;
+                    atomicOr(&abort_sh, kStatusRowOrderMismatch);
+                } else {
+                    r = static_cast<size_t>(listed);
+                    if ((a.mask[r] != 0) != (mk != 0)) atomicOr(&abort_sh, kStatusRowOrderMismatch);
+                }
             } else {
-                mk = a.mask[r];
+                mk = a.mask[r] != 0;
             }
             meta_row[i] = static_cast<int>(r);
-            meta_mask[i] = mk != 0;
-            if (mk != 0) {
+            meta_mask[i] = static_cast<unsigned char>(mk);
+            if (mk == 1) {
                 const long long seq = (a.row_offset + static_cast<long long>(r)) / a.tokens_per_seq;
                 meta_sel[i] = a.selected[r];
                 meta_old[i] = a.logp_old[r];
@@ -509,9 +509,9 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
         // ---- consumer warps
         for (int k_row = 0; k_row < batch_rows; k_row++) {
             const size_t row = static_cast<size_t>(meta_row[k_row]);
-            GRPO_TL(0);  // row start
             float4* out = reinterpret_cast<float4*>(a.dlogits + row * static_cast<size_t>(a.P)) + c0;
 
+            if (meta_mask[k_row] == 2) continue;  // a row index outside the batch: skipped by producer and consumers alike
             if (meta_mask[k_row] == 0) {  // uniform over the cluster: no barrier is reached
                 const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
@@ -546,7 +546,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                     for (int jj = 0; jj < TJ; jj++) x[k * TJ + jj] = make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
                 }
             }
-            GRPO_TL(1);  // ring -> registers done
 
             // ---- the selected logit, read back from the stage that holds its chunk
             int sel = 0;
@@ -639,7 +638,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             // are among them, and those are the terms whose fp32 error (~1e-7 each) the
             // log-sum-exp cannot absorb.  Everything else is light enough to average out.
             const double s_fixed = s_thread + (term_correction(m, shift) + term_correction(m2, shift));
-            GRPO_TL(2);  // exp + compensated sums done
             const double s_warp = warp_sum_all(s_fixed);
             if (CHECK) chk = warp_sum_f(chk);
 
@@ -667,7 +665,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                     send_part(&parts[row_parity][crank * WARPS + warp], &xbar[row_parity], static_cast<unsigned>(lane),
                               s_warp, m_warp, shift, chk, xs0, hs0);
             }
-            GRPO_TL(3);  // partial handed over
 
             // ---- warp 0 of every CTA combines all partials of the row: same slots, same order,
             //      same bits in every CTA.  Factors in double, fixed shuffle trees.
@@ -678,7 +675,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                     alive = CLUSTER > 1 ? mbar_wait_cluster(&xbar[row_parity], xuses[row_parity] & 1u)
                                         : mbar_wait(&xbar[row_parity], xuses[row_parity] & 1u);
                 xuses[row_parity]++;
-                GRPO_TL(4);  // all partials have landed (thread 0 only)
                 const WarpPart* in = parts[row_parity];
                 float m_lane = kNegInf;
 #pragma unroll
@@ -708,7 +704,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                 const double z_row = warp_sum_all(s);
                 if (CHECK) c = warp_sum_f(c);
                 x_sel = warp_sum_f(xs);
-                GRPO_TL(5);  // row maximum and normaliser known (thread 0 only)
                 // ---- row leader: dlogp for the backward sweep and the row's record.  Every CTA of
                 //      the cluster repeats it on the same bits; rank 0 writes the record.
                 if (lane == 0)
@@ -717,7 +712,6 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                                          bad_sel || (CHECK && c != 0.0f) || !alive, crank == 0);
             }
             consumer_sync(THREADS);
-            GRPO_TL(6);  // leader done, everyone past the second block barrier
             // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
             const RowBroadcast b = bc;
             const float coef = static_cast<float>(warp_f[warp]) * b.neg_g_over_z;
@@ -757,14 +751,13 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             }
             // same thread, same address, program order: this store lands after the vector store above
             if (owns_sel) a.dlogits[row * static_cast<size_t>(a.P) + b.selected] = fmaf(e_sel, coef, b.g);
-            GRPO_TL(7);  // stores issued
             row_parity ^= 1u;
         }  // rows of the batch
     }      // batches
 
     // ---- shutdown: nothing may still be landing in this CTA's shared memory when it retires
     if (tid == 0) q_cons_final = q;
-    if (!alive) abort_sh = 1;
+    if (!alive) atomicOr(&abort_sh, kStatusPipelineTimeout);
     __syncthreads();
     if (is_producer && lane == 0) {
         unsigned qc = q_cons_final;
@@ -772,7 +765,8 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             mbar_wait(&full_bar[qc % STAGES], (qc / STAGES) & 1u);
             qc++;
         }
-        if (abort_sh != 0) *a.status = 1;
+        // the pass's status word was cleared by block 0's first instruction, long before any CTA gets here
+        if (abort_sh != 0) atomicOr(a.status, abort_sh);
     }
     if (CLUSTER > 1) cg::this_cluster().sync();  // no CTA retires while a peer may still push into its inbox
 }
@@ -981,7 +975,9 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
     }
     block_sum<kReduceThreads, 5>(t, scratch);
     if (tid == 0) {
-        if (*a.status != 0) t[4] = -1.0;
+        const int status = *a.status;
+        if (status & kStatusRowOrderMismatch) t[4] = kBadInputsRowOrder;
+        if (status & kStatusPipelineTimeout) t[4] = kBadInputsPipelineTimeout;
         if (x.world <= 0) {
             a.result->loss = t[0];
             a.result->pg_loss = t[1];
@@ -1033,7 +1029,7 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
     const long long start = clock64();
     for (long long i = tid; i < n; i += kReduceThreads) {
         double s = 0.0;
-        bool negative = false;
+        double worst = 0.0;  // the most negative term: some rank's pass failed (-1 pipeline, -3 row order)
         for (int q = 0; q < x.world; q++) {
             const unsigned long long* src = exchange_slot(x.peers[x.rank], stride, buf, q) + 2 * i;
             unsigned long long w0, w1;
@@ -1041,7 +1037,7 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
                 asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w0) : "l"(src) : "memory");
                 asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w1) : "l"(src + 1) : "memory");
                 if ((w0 & 0xffffffff00000000ULL) == tag && (w1 & 0xffffffff00000000ULL) == tag) break;
-                if (timed_out || clock64() - start > (1LL << 32)) {  // about two seconds: a peer is gone
+                if (timed_out || clock64() - start > x.timeout_cycles) {  // a peer is gone (or very late)
                     timed_out = 1;
                     w0 = w1 = 0ULL;
                     break;
@@ -1049,11 +1045,11 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
                 __nanosleep(32);
             }
             const double term = __longlong_as_double(static_cast<long long>((w0 & 0xffffffffULL) | (w1 << 32)));
-            negative = negative || term < 0.0;
+            worst = fmin(worst, term);
             s += term;
         }
         if (i < 5) {
-            if (i == 4 && negative) s = -1.0;  // some rank's pipeline gave up
+            if (i == 4 && worst < 0.0) s = worst > -2.0 ? kBadInputsPipelineTimeout : kBadInputsRowOrder;
             record[i] = s;
         } else {
             global_lengths[i - 5] = s;
@@ -1061,7 +1057,7 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
         }
     }
     __syncthreads();
-    if (tid < 5) out[tid] = (tid == 4 && timed_out) ? -2.0 : record[tid];  // -2: some rank never answered
+    if (tid < 5) out[tid] = (tid == 4 && timed_out) ? kBadInputsExchangeTimeout : record[tid];  // some rank never answered
     block_weights<kReduceThreads>(global_lengths, x.n_seq, x.reduction, x.length_alpha, x.weights_out, x.meta_out,
                                   scratch);
 }
@@ -1100,7 +1096,8 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
     auto kernel = logits_pipelined_kernel<THREADS, VEC, TJ, STAGES, CLUSTER, CHECK>;
     constexpr size_t ring_bytes = static_cast<size_t>(STAGES) * TJ * THREADS * sizeof(float4);
     // per device: opt in to the large dynamic shared memory and find how many clusters fit at once
-    static int clusters_cached[64] = {0};
+    // (two host threads may fill the same entry at once: both compute the same number)
+    static std::atomic<int> clusters_cached[64];
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
@@ -1118,7 +1115,7 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
     cfg.attrs = attr;
     cfg.numAttrs = CLUSTER > 1 ? 1 : 0;
 
-    int max_clusters = clusters_cached[dev];
+    int max_clusters = clusters_cached[dev].load(std::memory_order_acquire);
     if (max_clusters == 0) {
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_bytes));
         if (err != cudaSuccess) return err;
@@ -1137,7 +1134,7 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
             if (err != cudaSuccess) return err;
         }
         if (max_clusters < 1) return cudaErrorLaunchOutOfResources;
-        clusters_cached[dev] = max_clusters;
+        clusters_cached[dev].store(max_clusters, std::memory_order_release);
     }
     const long long clusters = a.n_rows < max_clusters ? a.n_rows : max_clusters;
     cfg.gridDim = dim3(static_cast<unsigned>(clusters * CLUSTER), 1, 1);
@@ -1178,15 +1175,15 @@ bool variant_fits(int variant, int P) {
 
 }  // namespace
 
-#ifdef GRPO_TIMELINE
-extern "C" int grpo_b200_debug_timeline(long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(g_timeline)) == cudaSuccess ? 0 : 3;
+// Test and tuning hook (process-wide): -1 restores the dispatcher's own choice.
+namespace {
+std::atomic<int> g_forced_variant{-1};
 }
-extern "C" int grpo_b200_debug_grid() {
-    int g = -1;
-    return cudaMemcpyFromSymbol(&g, g_timeline_grid, sizeof(g)) == cudaSuccess ? g : -1;
+int set_forced_variant(int variant) {
+    if (variant >= kNumVariants) return -1;
+    g_forced_variant.store(variant < 0 ? -1 : variant, std::memory_order_relaxed);
+    return 0;
 }
-#endif
 
 int resident_variant_count() { return kNumVariants; }
 
@@ -1195,12 +1192,13 @@ const char* resident_variant_name(int variant) {
 }
 
 // Returns the variant index for this row layout, or -1 when only the streaming kernel applies.
-int pick_resident_variant(const void* logits, const void* dlogits, int V, int P) {
+int pick_resident_variant(const void* logits, const void* dlogits, int V, int P, long long n_rows) {
     (void)V;
+    (void)n_rows;
     if ((P & 3) != 0) return -1;
     if ((reinterpret_cast<uintptr_t>(logits) & 15u) || (reinterpret_cast<uintptr_t>(dlogits) & 15u)) return -1;
-    if (g_forced_variant >= 0 && g_forced_variant < kNumVariants)
-        return variant_fits(g_forced_variant, P) ? g_forced_variant : -1;
+    const int forced = g_forced_variant.load(std::memory_order_relaxed);
+    if (forced >= 0 && forced < kNumVariants) return variant_fits(forced, P) ? forced : -1;
     // smallest CTAs whose cluster (at most 8) holds the row: four CTAs per SM overlap one another's serial phases
     static const int order[] = {14, 15, 16, 17, 7, 3};
     for (int idx : order)

@@ -266,18 +266,37 @@ def logits_sharded(logits_t: torch.Tensor, logp_old, logp_ref, selected, advanta
 
 def lengths_sharded(mask: torch.Tensor, n_seq: int, tokens_per_seq: int, row_offset: int, *, exchange: PeerExchange,
                     reduction: int, length_alpha: float, weights: torch.Tensor, meta: torch.Tensor,
-                    workspace: torch.Tensor, lengths: torch.Tensor | None = None) -> torch.Tensor:
+                    workspace: torch.Tensor, status: torch.Tensor, lengths: torch.Tensor | None = None) -> torch.Tensor:
     """Global per-response lengths of ``mask`` (this rank's rows) summed over the ranks through their
     exchange regions, and the weights derived from them: what the first pass needs, without a
-    collective call.  Counts as one pass of the region."""
+    collective call.  ``status`` (five doubles) receives the exchanged record: zeros, or
+    ``bad_inputs = -2`` when a rank did not answer in time.  Counts as one pass of the region."""
+    if n_seq != exchange.n_seq:
+        raise ValueError(f"n_seq is {n_seq} but the exchange region was created for {exchange.n_seq} responses")
     exchange.passes += 1
     _lib.check(_lib.lib().grpo_b200_lengths_sharded(
         _check_tensor(mask, torch.int32, "mask"), mask.numel(), row_offset, tokens_per_seq, n_seq, exchange.regions,
         exchange.rank, exchange.world, int(reduction), float(length_alpha),
         _check_tensor(weights, torch.float32, "weights"), _check_tensor(meta, torch.int32, "meta"),
         None if lengths is None else _check_tensor(lengths, torch.float64, "lengths"),
-        workspace.data_ptr(), workspace.numel(), _stream()))
+        _check_tensor(status, torch.float64, "status"), workspace.data_ptr(), workspace.numel(), _stream()))
     return weights
+
+
+def set_exchange_timeout_cycles(cycles: int) -> None:
+    """Process-wide limit of the exchange's wait for the other ranks, in SM clock cycles."""
+    _lib.check(_lib.lib().grpo_b200_exchange_set_timeout_cycles(int(cycles)))
+
+
+def synthetic_logits(out: torch.Tensor, V: int, scale: float, seed: int, *, row_offset: int = 0,
+                     tail_fill: float = 123.0) -> torch.Tensor:
+    """Fills ``out`` (``[n_rows, P]`` fp32) with the counter-based synthetic logits of global rows
+    ``[row_offset, row_offset + n_rows)``; :func:`..workloads.synthetic_logits_rows` is the host
+    restatement of the same function."""
+    n_rows, P = out.shape
+    _lib.check(_lib.lib().grpo_b200_synthetic_logits(_check_tensor(out, torch.float32, "logits"), n_rows, row_offset,
+                                                    V, P, float(scale), int(seed), float(tail_fill), _stream()))
+    return out
 
 
 def sample_rows(logits_t: torch.Tensor, V: int, rows: torch.Tensor, *, coins: torch.Tensor | None = None,
@@ -320,7 +339,7 @@ def plan(logits_t: torch.Tensor, V: int, kernel: int = CudaLogitsKernel.fused,
     """Name of the kernel the dispatcher runs for this layout."""
     d = logits_t if dlogits is None else dlogits
     return _lib.lib().grpo_b200_logits_plan(logits_t.data_ptr(), d.data_ptr(), V, logits_t.shape[1],
-                                            int(kernel)).decode()
+                                            logits_t.shape[0], int(kernel)).decode()
 
 
 class ResidentBoundary:

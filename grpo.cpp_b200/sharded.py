@@ -121,6 +121,8 @@ class ShardedBoundary:
         self.result = self.xchg[:5]
         self.lengths_f64 = self.xchg[5:]
         self.workspace = ops.logits_workspace(self.n_local, device)
+        # the record of prepare()'s own exchange: zeros unless a rank did not answer (bad_inputs = -2)
+        self.prepare_status = torch.zeros(5, dtype=torch.float64, device=device)
         self.exchange = None  # set by enable_peer_exchange
         self.row_order = None  # set by prepare: the upcoming pass's balanced row order
 
@@ -135,7 +137,8 @@ class ShardedBoundary:
         if self.exchange is not None:  # through the ranks' regions: no collective call
             self.ops.lengths_sharded(mask_local, self.S, self.T, self.row_offset, exchange=self.exchange,
                                      reduction=self.reduction, length_alpha=self.alpha, weights=self.weights,
-                                     meta=self.meta, workspace=self.workspace, lengths=self.lengths_f64)
+                                     meta=self.meta, workspace=self.workspace, status=self.prepare_status,
+                                     lengths=self.lengths_f64)
         else:
             self.ops.count_lengths(mask_local, self.S, self.T, self.row_offset, self.lengths)
             self._all_reduce(self.lengths)
@@ -227,13 +230,17 @@ class ShardedBoundary:
     def stats(self) -> dict:
         """Reads the records back (synchronises) and applies the reference's error contract
         (src/cuda/grpo_loss_cuda.cu:44-46, 814-815) to the GLOBAL quantities."""
-        meta = self.meta.tolist()
-        res = self.result.tolist()
+        # one read-back: the pass's record, prepare()'s record and the two counters
+        host = torch.cat([self.result, self.prepare_status, self.meta.to(torch.float64)]).tolist()
+        res, prep, meta = host[:5], host[5:10], [int(host[10]), int(host[11])]
+        if prep[4] < 0:  # the lengths exchange itself failed: the weights came from partial counts
+            raise RuntimeError("the exchange between ranks timed out")
+        if res[4] < 0:
+            raise RuntimeError({-1.0: "a pipeline wait timed out on some rank",
+                                -2.0: "the exchange between ranks timed out"}.get(
+                                    res[4], "the row order does not belong to the mask"))
         if meta[1] != 0:
             raise RuntimeError("every sequence needs at least one valid token")
-        if res[4] < 0:
-            raise RuntimeError("a pipeline wait timed out on some rank" if res[4] > -2 else
-                               "the exchange between ranks timed out")
         if res[4] != 0:
             raise RuntimeError("selected token is outside the vocabulary")
         loss, pg, kl = (float(torch.tensor(v, dtype=torch.float64).to(torch.float32)) for v in res[:3])

@@ -239,3 +239,37 @@ def reference_logits_fixture(B: int, G: int, T: int, V: int, partial: bool) -> L
     ref = np.where(active, (now + f(0.01) * ((row % 5) - 2).astype(f)).astype(f), f(0)).astype(f)
     return LogitsBatch(B, G, T, V, logits, old, ref, selected, adv, mask, 0.2, 0.0,
                        SEQUENCE_MEAN, 0.0, f"ref-logits-fixture-{B}x{G}x{T}x{V}")
+
+
+# Counter-based synthetic logits, host restatement of the library's grpo_b200_synthetic_logits kernel
+# (csrc/synthetic.cu): element (r, v) of a batch with row stride P depends on (seed, r, v) only, so a
+# host can rebuild any row of a batch that exists only on the devices, whatever the sharding.
+_GAMMA = np.uint64(0x9E3779B97F4A7C15)
+_M1 = np.uint64(0xBF58476D1CE4E5B9)
+_M2 = np.uint64(0x94D049BB133111EB)
+
+
+def synthetic_scale(sigma: float) -> np.float32:
+    """The fp32 factor that gives the sum of eight 16-bit uniforms standard deviation ``sigma``."""
+    return np.float32(sigma / np.sqrt(8.0 * (65536.0 ** 2 - 1.0) / 12.0))
+
+
+def _mix64(z: np.ndarray) -> np.ndarray:
+    z = (z ^ (z >> np.uint64(30))) * _M1
+    z = (z ^ (z >> np.uint64(27))) * _M2
+    return z ^ (z >> np.uint64(31))
+
+
+def _fields16(h: np.ndarray) -> np.ndarray:
+    m = np.uint64(0xFFFF)
+    return ((h & m) + ((h >> np.uint64(16)) & m) + ((h >> np.uint64(32)) & m) + (h >> np.uint64(48))).astype(np.int64)
+
+
+def synthetic_logits_rows(rows, V: int, P: int, scale, seed: int) -> np.ndarray:
+    """``[len(rows), V]`` fp32: the vocabulary columns of the given GLOBAL rows."""
+    rows = np.asarray(rows, np.uint64).reshape(-1, 1)
+    with np.errstate(over="ignore"):
+        c = rows * np.uint64(P) + np.arange(V, dtype=np.uint64)[None, :]
+        s = np.uint64(seed) + (np.uint64(2) * c + np.uint64(1)) * _GAMMA
+        k = _fields16(_mix64(s)) + _fields16(_mix64(s + _GAMMA)) - 262140
+    return k.astype(np.float32) * np.float32(scale)

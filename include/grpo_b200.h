@@ -80,7 +80,10 @@ typedef struct {
     double bad_grads; /* number of active tokens whose gradient is non-finite  */
     double bad_inputs;/* selected-token path: active tokens with a non-finite log-probability or
                          a mask value other than 0/1; logits path: active rows with an
-                         out-of-vocabulary selected id or (when checked) a non-finite logit */
+                         out-of-vocabulary selected id or (when checked) a non-finite logit.
+                         Logits path, negative values: the pass itself failed and the other fields
+                         mean nothing -- -1 a bounded wait of the copy pipeline gave up, -2 a rank
+                         did not answer the exchange in time, -3 row_order does not belong to mask */
 } grpo_b200_result_t;
 
 const char* grpo_b200_last_error(void);
@@ -183,7 +186,10 @@ int grpo_b200_loss_noalloc(const float* logp_new, const float* logp_old, const f
  * selected_logp (nullable) receives log p(selected) per row (0 for masked rows).
  * row_order (nullable) is the output of grpo_b200_row_order for this mask: with it the row
  * kernel deals every cluster the same number of active and of masked rows, evenly interleaved,
- * instead of every n-th row whatever its mask; results do not depend on it. */
+ * instead of every n-th row whatever its mask; results do not depend on it.  A row order made
+ * from another mask is detected (counts that do not add up, row indices outside the batch, a
+ * listed row whose mask value disagrees) and reported as bad_inputs = -3; no access leaves the
+ * batch because of it. */
 size_t grpo_b200_logits_workspace_bytes(int64_t n_rows);
 int grpo_b200_logits(const float* logits, float* dlogits, const float* logp_old,
                      const float* logp_ref, const int32_t* selected, const float* advantages,
@@ -220,11 +226,19 @@ int grpo_b200_row_order(const int32_t* mask, int64_t n_rows, int32_t* order,
  * (next_weights may be the buffer `weights` points to), and next_lengths[n_seq] (nullable) the
  * global counts as doubles.  The sums are taken in rank order, so every rank gets the same
  * bits.  The region counts its own passes on the device; the ranks must make the same sequence
- * of calls on their regions.  A rank whose peers do not answer within about two seconds stops
- * waiting and reports bad_inputs = -2; nothing blocks forever.  world = 1 runs the same code
+ * of calls on their regions, with the n_seq their regions were created for (checked against the
+ * own region).  A rank whose peers do not answer within the exchange timeout (about two seconds
+ * of SM clock unless grpo_b200_exchange_set_timeout_cycles changed it) stops waiting and reports
+ * bad_inputs = -2; nothing blocks forever.  The timeout treats a late peer like a lost one, and a
+ * rank that gave up runs ahead of the others: line the ranks up on the host (a barrier of whatever
+ * process group they share) before the first call on a batch and after any host-side stall such
+ * as a checkpoint, and treat -2 as fatal for the regions involved.  world = 1 runs the same code
  * against the own region alone. */
 size_t grpo_b200_exchange_bytes(int64_t n_seq);
 int grpo_b200_exchange_create(int64_t n_seq, void** region);
+/* Process-wide limit of the exchange's wait for the other ranks, in SM clock cycles (default 2^32,
+ * about two seconds; no counterpart in the reference).  Read when a sharded call is enqueued. */
+int grpo_b200_exchange_set_timeout_cycles(int64_t cycles);
 int grpo_b200_exchange_export(void* region, unsigned char handle[64]);
 int grpo_b200_exchange_open(const unsigned char handle[64], void** peer_region);
 int grpo_b200_exchange_close(void* peer_region);
@@ -246,13 +260,15 @@ int grpo_b200_logits_sharded(const float* logits, float* dlogits, const float* l
  * exchange of grpo_b200_logits_sharded, with an all-zero record) and derives the weights.
  * Replaces make_weights (src/cuda/grpo_loss_cuda.cu:21-57) for a batch whose rows are spread
  * over ranks.  weights[n_seq], meta[2] and lengths[n_seq] (nullable) as in
- * grpo_b200_logits_sharded; workspace as for grpo_b200_logits on n_rows rows.  Counts as one
- * pass of the region: every rank makes the call. */
+ * grpo_b200_logits_sharded; workspace as for grpo_b200_logits on n_rows rows.  status (a device
+ * record, required) receives the exchanged record: all zeros, or bad_inputs = -2 when a rank did
+ * not answer in time -- the weights then come from partial counts and must not be used.  Counts as
+ * one pass of the region: every rank makes the call. */
 int grpo_b200_lengths_sharded(const int32_t* mask, int64_t n_rows, int64_t row_offset,
                               int tokens_per_seq, int64_t n_seq, void* const* regions, int rank,
                               int world, int reduction, float length_alpha, float* weights,
-                              int32_t* meta, double* lengths, void* workspace,
-                              size_t workspace_bytes, grpo_b200_stream_t stream);
+                              int32_t* meta, double* lengths, grpo_b200_result_t* status,
+                              void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream);
 
 /* Sampling and log-probability extraction on logits that stay on the device.  Replaces, for
  * the rows named in rows[n_selected] (indices into the [n_rows][P] logits), the host-side
@@ -272,13 +288,25 @@ int grpo_b200_sample_rows(const float* logits, int64_t n_rows, int V, int P, con
                           int32_t* tokens_out, float* logp_out, double* lse_out,
                           grpo_b200_stream_t stream);
 
-/* Tuning hook for benchmarks: force the row-resident kernel variant (index into the table
- * printed by grpo_b200_logits_variant_name), or -1 for the built-in choice.  Process-wide. */
+/* Counter-based synthetic logits for benchmarks and tests: element (row_offset + r, v) of a batch
+ * with row stride P is a pure function of (seed, global row, column) -- the sum of eight 16-bit
+ * fields of two splitmix64 outputs, centred, times `scale` (one fp32 multiply) -- so any split of
+ * the batch over ranks builds the same rows and a host can rebuild any row bit for bit.  Columns
+ * [V, P) receive tail_fill.  Stands where the reference builds its arithmetic fixtures on the
+ * host and copies them over (bench/bench_grpo_loss_cuda.cu:60-102). */
+int grpo_b200_synthetic_logits(float* logits, int64_t n_rows, int64_t row_offset, int V, int P,
+                               float scale, uint64_t seed, float tail_fill,
+                               grpo_b200_stream_t stream);
+
+/* Test and tuning hook: force the row-resident kernel variant (index into the table printed by
+ * grpo_b200_logits_variant_name), or -1 for the built-in choice.  Process-wide; not for use while
+ * other threads are inside the library. */
 int grpo_b200_logits_set_variant(int variant);
 /* Name ("cluster x threads x vec") of variant i, NULL past the end of the table. */
 const char* grpo_b200_logits_variant_name(int variant);
-/* Name of the kernel the dispatcher would run for this row layout and selector. */
-const char* grpo_b200_logits_plan(const void* logits, const void* dlogits, int V, int P, int kernel);
+/* Name of the kernel the dispatcher would run for this row layout, row count and selector. */
+const char* grpo_b200_logits_plan(const void* logits, const void* dlogits, int V, int P,
+                                  int64_t n_rows, int kernel);
 
 /* ------------------------------------------------------------------------------------
  * HOST LAYER (reference-facing; host arrays in, host results out, synchronous)

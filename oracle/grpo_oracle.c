@@ -92,6 +92,36 @@ int grpo_oracle_group_advantages(const float* rewards, int B, int G, int mode, f
     return GRPO_ORACLE_OK;
 }
 
+/* One active token (src/cpu/grpo_loss.cpp:137-160): terms = {w*loss, w*pg, w*kl} as fp32 products,
+ * returns w * dL/dlogp. */
+static float one_token(float lp_new, float lp_old, float lp_ref, float A, float w, float lo, float hi,
+                       float beta, float terms[3]) {
+    float pg = 0.0f, pg_grad = 0.0f;
+    if (A != 0.0f) { /* zero advantage never evaluates the ratio (:139) */
+        float rho = expf(lp_new - lp_old);
+        float rho_c = rho < lo ? lo : (hi < rho ? hi : rho);
+        float u = rho * A, c = rho_c * A;
+        pg = -(c < u ? c : u);
+        /* strictly outside the clip window on the side the advantage pushes to:
+         * no gradient; the boundary itself keeps the ratio branch (:144-147) */
+        int cut_hi = A > 0.0f && rho > hi;
+        int cut_lo = A < 0.0f && rho < lo;
+        pg_grad = (cut_hi || cut_lo) ? 0.0f : -A * rho;
+    }
+
+    /* k3 estimator of KL(new || ref) on the sampled token (:150-155) */
+    float d = lp_ref - lp_new;
+    float em1 = expm1f(d);
+    float kl = em1 - d;
+    float loss = pg + beta * kl;
+    float kl_grad = -beta * em1;
+
+    terms[0] = w * loss;
+    terms[1] = w * pg;
+    terms[2] = w * kl;
+    return w * (pg_grad + kl_grad);
+}
+
 /* src/cpu/grpo_loss.cpp:60-174 */
 int grpo_oracle_loss(const float* lp_new, const float* lp_old, const float* lp_ref,
                      const float* adv, const int* mask, int B, int G, int T,
@@ -150,31 +180,12 @@ int grpo_oracle_loss(const float* lp_new, const float* lp_old, const float* lp_r
             size_t i = s * (size_t)T + (size_t)t;
             if (mask[i] == 0) continue;
 
-            float pg = 0.0f, pg_grad = 0.0f;
-            if (A != 0.0f) { /* zero advantage never evaluates the ratio (:139) */
-                float rho = expf(lp_new[i] - lp_old[i]);
-                float rho_c = rho < lo ? lo : (hi < rho ? hi : rho);
-                float u = rho * A, c = rho_c * A;
-                pg = -(c < u ? c : u);
-                /* strictly outside the clip window on the side the advantage pushes to:
-                 * no gradient; the boundary itself keeps the ratio branch (:144-147) */
-                int cut_hi = A > 0.0f && rho > hi;
-                int cut_lo = A < 0.0f && rho < lo;
-                pg_grad = (cut_hi || cut_lo) ? 0.0f : -A * rho;
-            }
-
-            /* k3 estimator of KL(new || ref) on the sampled token (:150-155) */
-            float d = lp_ref[i] - lp_new[i];
-            float em1 = expm1f(d);
-            float kl = em1 - d;
-            float loss = pg + beta * kl;
-            float kl_grad = -beta * em1;
-
+            float terms[3];
+            dlogp[i] = one_token(lp_new[i], lp_old[i], lp_ref[i], A, w, lo, hi, beta, terms);
             /* fp32 products, double running totals (:157-160) */
-            sum_loss += w * loss;
-            sum_pg += w * pg;
-            sum_kl += w * kl;
-            dlogp[i] = w * (pg_grad + kl_grad);
+            sum_loss += terms[0];
+            sum_pg += terms[1];
+            sum_kl += terms[2];
         }
     }
     free(len);
@@ -249,6 +260,48 @@ done:
     free(sel_logp);
     free(dlogp);
     return rc;
+}
+
+/* The per-row steps of grpo_oracle_logits for rows taken out of a batch that is too large to hold
+ * on the host: forward (src/cpu/grpo_loss.cpp:200-216), token loss (:137-160) and backward
+ * (:223-237) of each given row, with its response's advantage and weight passed in (the caller
+ * derives the weight from the whole batch's mask with the expressions of :124-131). */
+int grpo_oracle_logits_rows(const float* rows, int n, int V, const float* lp_old, const float* lp_ref,
+                            const int* selected, const float* adv, const float* w, float clip_eps,
+                            float beta, float* dlogits, float* sel_logp_out, float* terms_out) {
+    if (n <= 0) return GRPO_ORACLE_E_DIMS;
+    if (V <= 0) return GRPO_ORACLE_E_VOCAB;
+    if (clip_eps < 0.0f || clip_eps >= 1.0f || !isfinite(clip_eps)) return GRPO_ORACLE_E_CLIP;
+    if (beta < 0.0f || !isfinite(beta)) return GRPO_ORACLE_E_BETA;
+    const size_t vocab = (size_t)V;
+    const float lo = 1.0f - clip_eps;
+    const float hi = 1.0f + clip_eps;
+    for (int i = 0; i < n; i++) {
+        int sel = selected[i];
+        if (sel < 0 || sel >= V) return GRPO_ORACLE_E_SELECTED;
+        const float* row = rows + (size_t)i * vocab;
+        float* out = dlogits + (size_t)i * vocab;
+        double top = row[0];
+        for (int v = 0; v < V; v++) {
+            if (!isfinite(row[v])) return GRPO_ORACLE_E_LOGITS;
+            double x = (double)row[v];
+            top = top < x ? x : top;
+        }
+        double z = 0.0;
+        for (int v = 0; v < V; v++) z += exp((double)row[v] - top);
+        double lse = top + log(z);
+        float sel_logp = (float)((double)row[sel] - lse);
+        if (sel_logp_out) sel_logp_out[i] = sel_logp;
+        float g = one_token(sel_logp, lp_old[i], lp_ref[i], adv[i], w[i], lo, hi, beta, terms_out + 3 * (size_t)i);
+        memset(out, 0, vocab * sizeof(float));
+        if (g == 0.0f) continue;
+        double x_sel = row[sel];
+        for (int v = 0; v < V; v++) {
+            double p = exp((double)row[v] - x_sel + sel_logp);
+            out[v] = g * ((v == sel ? 1.0f : 0.0f) - (float)p);
+        }
+    }
+    return GRPO_ORACLE_OK;
 }
 
 /* apps/04_gpt2_grpo.cu:61-66 */

@@ -75,11 +75,22 @@ int grpo_oracle_logits(const float* logits, const float* logp_old, const float* 
                        float* dlogits_out, float* stats_out, int* valid_tokens_out,
                        float* selected_logp_out);
 
+/* The same per-row steps as grpo_oracle_logits (forward :200-216, token loss :137-160, backward
+ * :223-237) for n rows taken out of a larger batch, with each row's advantage and weight given
+ * by the caller.  rows [n][V]; dlogits_out [n][V]; sel_logp_out [n] (nullable); terms_out [n][3]
+ * = the fp32 products {w*loss, w*pg, w*kl} the reference adds to its double totals.  Checked in
+ * tests against grpo_oracle_logits on whole small batches (same bits). */
+int grpo_oracle_logits_rows(const float* rows, int n, int V, const float* logp_old,
+                            const float* logp_ref, const int* selected, const float* adv,
+                            const float* w, float clip_eps, float beta, float* dlogits_out,
+                            float* sel_logp_out, float* terms_out);
+
 /* Sampling helpers of the reference's GPT-2 demo, restated: apps/04_gpt2_grpo.cu:61-66
- * (row_logsumexp) and :68-80 (sample_row, with the uniform number passed in instead of drawn
- * from std::mt19937 inside).  Parity of these two: UNPINNED -- the demo is one translation unit
- * with the absent llm.c model code, so its object code cannot be built here, and the reference
- * has no test or golden vector for them; they are pinned by known answers only. */
+ * (row_logsumexp) and :68-78 (sample_row, with the uniform number passed in instead of drawn
+ * from std::mt19937 inside).  Parity of these two: PINNED -- oracle/Makefile cuts the two helpers
+ * out of the reference file at build time and compiles them behind ref_sample_shim.cpp; the
+ * committed vectors (tests/golden/sampling_cases.npz: log-sum-exp bits, the generator's coins,
+ * drawn tokens) come from that object code, and the restatement reproduces them exactly. */
 double grpo_oracle_row_logsumexp(const float* row, int V);
 int grpo_oracle_sample_row(const float* row, int V, double coin);
 

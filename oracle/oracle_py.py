@@ -80,6 +80,8 @@ class _Lib:
         if kind == "port":
             self.lib.grpo_oracle_strerror.restype = C.c_char_p
             self.lib.grpo_oracle_strerror.argtypes = [C.c_int]
+            self.lib.grpo_oracle_logits_rows.argtypes = [_fp, C.c_int, C.c_int, _fp, _fp, _ip, _fp, _fp, C.c_float,
+                                                         C.c_float, _fp, _fp, _fp]
             self.lib.grpo_oracle_row_logsumexp.restype = C.c_double
             self.lib.grpo_oracle_row_logsumexp.argtypes = [_fp, C.c_int]
             self.lib.grpo_oracle_sample_row.restype = C.c_int
@@ -103,6 +105,20 @@ class _Lib:
         """apps/04_gpt2_grpo.cu:68-80 with the uniform number given (port only; unpinned)."""
         r = _as(row, _f)
         return int(self.lib.grpo_oracle_sample_row(r.ctypes.data_as(_fp), r.size, float(coin)))
+
+    def logits_rows(self, rows, logp_old, logp_ref, selected, adv, w, clip_eps=0.2, beta=0.0):
+        """Rows out of a larger batch with their advantages and weights given (port only).
+        Returns ``(dlogits[n,V], selected_logp[n], terms[n,3])``."""
+        x = _as(rows, _f)
+        n, V = x.shape
+        b, c, sel = _as(logp_old, _f), _as(logp_ref, _f), _as(selected, np.int32)
+        a, ww = _as(adv, _f), _as(w, _f)
+        assert b.size == c.size == sel.size == a.size == ww.size == n
+        out, lp, terms = np.zeros((n, V), _f), np.zeros(n, _f), np.zeros((n, 3), _f)
+        self._check(self.lib.grpo_oracle_logits_rows(_p(x, _fp), n, V, _p(b, _fp), _p(c, _fp), _p(sel, _ip),
+                                                     _p(a, _fp), _p(ww, _fp), clip_eps, beta, _p(out, _fp),
+                                                     _p(lp, _fp), _p(terms, _fp)))
+        return out, lp, terms
 
     def group_advantages(self, rewards, B, G, mode=STANDARDIZED, eps=1e-8):
         r = _as(rewards, _f)

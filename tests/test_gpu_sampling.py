@@ -1,5 +1,7 @@
 """Parity of grpo_b200_sample_rows with the CPU restatement of the reference demo's host-side
-sampling (apps/04_gpt2_grpo.cu:61-80, 138-161) -- runs on the B200, through the C ABI.
+sampling (apps/04_gpt2_grpo.cu:61-78, 138-161; the restatement is pinned to the reference's object
+code by tests/test_oracle.py) and with vectors produced by that object code -- runs on the B200,
+through the C ABI.
 
 Tolerances: log-sum-exp within 1e-12 relative (both sides sum exp() of the same doubles, in a
 different order); fp32 log-probabilities within one unit in the last place of the difference

@@ -10,6 +10,8 @@ Every comparison between the restatement and reference output is exact (``==`` o
 import math
 import zlib
 
+import os
+
 import numpy as np
 import pytest
 
@@ -288,7 +290,7 @@ def test_port_equals_reference_advantages():
 
 
 def test_sampling_helpers_known_answers():
-    """row_logsumexp / sample_row (apps/04_gpt2_grpo.cu:61-80, unpinned restatement): uniform rows
+    """row_logsumexp / sample_row (restating apps/04_gpt2_grpo.cu:61-78): uniform rows
     have lse = x + log V and a coin u lands on floor(u * V); a one-hot-like row always returns its
     peak; a coin past the accumulated mass falls back to V - 1."""
     p = oracle_py.load("port")
@@ -306,12 +308,68 @@ def test_sampling_helpers_known_answers():
 
 
 def test_sampling_helpers_against_committed_vectors():
-    """tests/golden/sampling_cases.npz freezes the restatement of apps/04_gpt2_grpo.cu:61-80."""
+    """tests/golden/sampling_cases.npz holds what the REFERENCE's own object code of
+    apps/04_gpt2_grpo.cu:61-78 returned (tests/golden/make_sampling_golden.py): the restatement must
+    give the same log-sum-exp bits and, fed the coins the reference's generator produced, the same
+    tokens."""
     from conftest import Golden
     g = Golden("sampling_cases.npz")
     p = oracle_py.load("port")
+    assert "V50257" in g.cases
     for name in g.cases:
         c = g.case(name)
         for i in range(len(c["coins"])):
             assert p.row_logsumexp(c["logits"][i]) == c["lse"][i]
             assert p.sample_row(c["logits"][i], c["coins"][i]) == c["tokens"][i]
+            assert np.float32(np.float64(c["logits"][i][c["tokens"][i]]) - c["lse"][i]) == c["logp"][i]
+
+
+def test_sampling_helpers_against_reference_object_code_on_fresh_inputs():
+    """Where oracle/_ref/libgrpo_ref_sample.so exists (built from the reference tree): same bits and
+    same tokens on inputs that are not in the committed file, including the coin sequence of
+    std::uniform_real_distribution<double> over std::mt19937."""
+    import make_sampling_golden as M
+    if not os.path.exists(M.REF_SAMPLE):
+        pytest.skip("reference sampling helpers were not built in this checkout")
+    lib = M.load_reference_sampler()
+    p = oracle_py.load("port")
+    rng = np.random.default_rng(7)
+    for V in (5, 1000, 32768):
+        x = rng.normal(0, 2.5, (8, V)).astype(np.float32)
+        lse, coins, tokens = M.reference_draws(lib, x, seed=99 + V)
+        assert ((coins >= 0) & (coins < 1)).all()
+        for i in range(8):
+            assert p.row_logsumexp(x[i]) == lse[i]
+            cdf = np.cumsum(np.exp(x[i].astype(np.float64) - lse[i]))
+            if np.abs(cdf - coins[i]).min() > 1e-12:
+                assert p.sample_row(x[i], coins[i]) == tokens[i]
+
+
+def test_rows_entry_matches_the_whole_batch_entry_bit_for_bit():
+    """grpo_oracle_logits_rows (rows out of a batch, weights given) against grpo_oracle_logits on the
+    whole batch, for the three reductions: same gradient bits, same selected log-probabilities, and
+    the per-row fp32 products add up (in double, in row order) to the batch's three sums."""
+    from grpo_cpp_b200 import workloads as W
+    p = oracle_py.load("port")
+    for reduction, alpha in ((0, 0.0), (1, 0.0), (2, 0.5)):
+        b = W.logits_case(2, 3, 7, 33, sigma=2.0, min_len=1, reduction=reduction, length_alpha=alpha, seed=3)
+        stats, valid, want, want_lp = p.logits(b.logits, b.logp_old, b.logp_ref, b.selected, b.advantages, b.mask,
+                                               b.B, b.G, b.T, b.V, want_selected_logp=True, **b.cfg())
+        lengths = b.mask.reshape(b.S, b.T).sum(1)
+        f = np.float32
+        if reduction == 0:
+            w_seq = f(1.0) / (f(b.S) * lengths.astype(f))
+        elif reduction == 1:
+            w_seq = np.full(b.S, f(1.0) / f(valid), f)
+        else:
+            w_seq = np.array([np.float32(np.power(f(L), f(alpha) - f(1.0), dtype=f)) for L in lengths], f) / f(b.S)
+        rows = np.flatnonzero(b.mask == 1)
+        seq = rows // b.T
+        got, got_lp, terms = p.logits_rows(b.logits.reshape(b.N, b.V)[rows], b.logp_old[rows], b.logp_ref[rows],
+                                           b.selected[rows], b.advantages[seq], w_seq[seq], b.clip_eps, b.beta)
+        assert (got.view(np.uint32) == want.reshape(b.N, b.V)[rows].view(np.uint32)).all()
+        assert (got_lp.view(np.uint32) == want_lp[rows].view(np.uint32)).all()
+        sums = np.zeros(3)
+        for t in terms:
+            sums += t.astype(np.float64)
+        assert (sums.astype(f) == stats).all()
