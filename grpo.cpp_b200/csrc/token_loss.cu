@@ -388,11 +388,13 @@ namespace grpo_b200 {
 namespace {
 
 constexpr long long kNoAllocMaxTokens = 1LL << 24;  // 16,777,216 tokens per call
-constexpr int kNoAllocBlocks = 1024;                // per-block partial slots held by the library
+constexpr int kNoAllocBlocks = kLossMaxBlocks;      // as many partial slots as the ordinary entry point's grid can have
 
-// The scratch the ordinary entry point takes from its caller lives here instead: 1024 x 5 doubles
-// (40 KB) of per-block partial sums.  Every GPU that loads this library keeps the array until the
-// process exits.  In host code this name is only a handle for the runtime, not a device address.
+// The scratch the ordinary entry point takes from its caller lives here instead: 2048 x 5 doubles
+// (80 KB) of per-block partial sums -- the same number of slots, so both entry points cut a batch
+// into the same blocks and add the same partials in the same order.  Every GPU that loads this
+// library keeps the array until the process exits.  In host code this name is only a handle for
+// the runtime, not a device address.
 static __device__ __align__(256) double g_noalloc_partials[kNoAllocBlocks * kPartialWidth];
 
 std::mutex g_noalloc_mutex;
@@ -436,6 +438,8 @@ extern "C" int grpo_b200_loss_noalloc(const float* logp_new, const float* logp_o
 
     // Set-up, once per device and with that device current: ask the runtime where the array lives
     // on THIS device.  Passing the symbol itself to a kernel would hand it a host-side address.
+    // The address is kept for the life of the process: a cudaDeviceReset in between would leave it
+    // stale (the header says so).
     int dev = 0;
     GRPO_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) {

@@ -156,13 +156,17 @@ int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* lo
  * its device memory out of one slab at start-up and has accounted for every byte of it, or code
  * running where an allocation would stall the whole device (cudaMalloc synchronises with every
  * stream) or is simply forbidden by the host framework's memory policy.
- * Same arithmetic, kernels and results as grpo_b200_loss; the per-block partial sums go to a
- * 40 KB array that the library itself holds on every GPU it is loaded on (until the process
- * exits) instead of a caller workspace.  Limits and rules:
+ * Same arithmetic, kernels, grid and summation order as grpo_b200_loss, so the same bits in dlogp
+ * and in the result record at every size it accepts; the per-block partial sums go to an 80 KB
+ * array that the library itself holds on every GPU it is loaded on (until the process exits)
+ * instead of a caller workspace.  Limits and rules:
  *   - at most 16,777,216 tokens per call; larger calls are refused with GRPO_B200_E_INVALID and a
  *     message naming the limit (use grpo_b200_loss for those);
  *   - the first call on each device looks up the array's device address (no allocation, but a
  *     runtime query): make that first call before starting any stream capture on that device;
+ *   - the address found by that first call is kept until the process exits: after a
+ *     cudaDeviceReset of that device it is stale and this entry point must not be used again in
+ *     the process;
  *   - all calls on one device share the array, so two calls that can overlap on the GPU (different
  *     streams, no dependency between them) race on it and must be serialised by the caller; calls
  *     in the same stream are safe, and nothing needs clearing between calls;
@@ -298,7 +302,7 @@ int grpo_b200_synthetic_logits(float* logits, int64_t n_rows, int64_t row_offset
                                float scale, uint64_t seed, float tail_fill,
                                grpo_b200_stream_t stream);
 
-/* Test and tuning hook: force the row-resident kernel variant (index into the table printed by
+/* Test and tuning hook (no counterpart in the reference): force the row-resident kernel variant (index into the table printed by
  * grpo_b200_logits_variant_name), or -1 for the built-in choice.  Process-wide; not for use while
  * other threads are inside the library. */
 int grpo_b200_logits_set_variant(int variant);

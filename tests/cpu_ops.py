@@ -127,10 +127,11 @@ def logits_sharded(logits_t, logp_old, logp_ref, selected, advantages, weights, 
 
 
 def lengths_sharded(mask, n_seq, tokens_per_seq, row_offset, *, exchange, reduction, length_alpha, weights, meta,
-                    workspace, lengths=None):
+                    workspace, status, lengths=None):
     import torch.distributed as dist
     assert exchange.peers is not None, "regions must be mapped before the first pass"
     exchange.passes += 1
+    status.zero_()  # this stand-in's exchange cannot time out
     counts = count_lengths(mask, n_seq, tokens_per_seq, row_offset).to(torch.float64)
     if exchange.world > 1:
         dist.all_reduce(counts)
