@@ -631,6 +631,16 @@ def gpu_arm(args, spec: dict) -> None:
     h2d = sum(host[k].numel() * host[k].element_size() for k in host)
     cfg = G.LossConfig(CLIP_EPS, BETA, G.ReductionMode(spec["reduction"]), spec["alpha"])
     e2e_s = []
+    shard = None
+    if world > 1:
+        # the host-facing sharded call (C ABI grpo_b200_logits_sharded_host; C++ face grpo::ShardedLogitsBoundary):
+        # this rank's host metadata in, device logits in place, the global statistics out
+        from grpo_cpp_b200.api import ShardedLogits
+        shard = ShardedLogits(rank, world, B, Gn, T, V, P, off, cnt)
+        handles = [None] * world
+        dist.all_gather_object(handles, shard.handle())
+        shard.connect_ipc(handles)
+        sel_local = np.ascontiguousarray(batch.sel_h[off:off + cnt])
     for i in range(args.warmup + args.steps):
         restore()
         barrier()
@@ -639,16 +649,9 @@ def gpu_arm(args, spec: dict) -> None:
             # the reference-facing call itself: host vectors in, device logits in place, stats out
             st = G.grpo_logits_cuda_device_inplace(work, batch.old_h, batch.ref_h, batch.sel_h, batch.adv_h, mask_h,
                                                    B, Gn, T, V, P, cfg)
-            e2e_loss = st.loss
         else:
-            for k in host:
-                devt[k].copy_(host[k], non_blocking=True)
-            sb.prepare(devt["mask"])
-            if peer:
-                sb.step_peer(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
-            else:
-                sb.step(work, devt["old"], devt["ref"], devt["sel"], devt["adv"], devt["mask"])
-            e2e_loss = sb.stats()["loss"]
+            st = shard.run(work, batch.old_h, batch.ref_h, sel_local, batch.adv_h, batch.m_local, cfg)
+        e2e_loss = st.loss
         dt = time.perf_counter() - t0
         if i >= args.warmup:
             e2e_s.append(dt)
@@ -689,8 +692,8 @@ def gpu_arm(args, spec: dict) -> None:
             "e2e": {"value": N * args.steps / e2e_total, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 48, "ms_per_step": 1e3 * e2e_total / args.steps, "loss": e2e_loss,
                     "api": "grpo_logits_cuda_device_inplace (host metadata, device logits)" if world == 1 else
-                           ("ShardedBoundary.prepare+step_peer+stats from pinned host metadata (no collective call)"
-                            if peer else "ShardedBoundary.prepare+step+stats from pinned host metadata")},
+                           "grpo_b200_logits_sharded_host (this rank's host metadata, device logits; lengths exchange, "
+                           "row order, row kernel, reduce kernel with the record exchange, one read-back)"},
             # per pass and rank: the row kernel and the reduce kernel (+ lengths and weights kernels with NCCL)
             "gpu_launches": (2 if peer else 4) * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -704,6 +707,9 @@ def gpu_arm(args, spec: dict) -> None:
     if peer:
         barrier()  # no rank unmaps a region that another rank's kernel may still write to
         sb.exchange.close()
+    if shard is not None:
+        barrier()
+        shard.close()
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:

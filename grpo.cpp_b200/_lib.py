@@ -70,6 +70,13 @@ SIGNATURES = {
                                              _flt, _int, _flt, _int, _int, _f, _f]),
     "grpo_b200_benchmark_logits_host": (_int, [_f, _sz, _f, _sz, _f, _sz, _i, _sz, _f, _sz, _i, _sz, _int, _int,
                                                _int, _int, _flt, _flt, _int, _flt, _int, _int, _f, _f]),
+    "grpo_b200_shard_create": (_int, [_int, _int, _i64, _int, _int, _int, _i64, _i64, C.POINTER(_vp)]),
+    "grpo_b200_shard_export": (_int, [_vp, C.c_char_p]),
+    "grpo_b200_shard_connect_ipc": (_int, [_vp, C.c_char_p]),
+    "grpo_b200_shard_connect_local": (_int, [_vp, C.POINTER(_vp)]),
+    "grpo_b200_shard_destroy": (_int, [_vp]),
+    "grpo_b200_logits_sharded_host": (_int, [_vp, _vp, _f, _sz, _f, _sz, _i, _sz, _f, _sz, _i, _sz, _flt, _flt, _int,
+                                             _flt, _int, _f, C.POINTER(_int)]),
     "grpo_b200_release_cache": (_int, []),
 }
 

@@ -190,3 +190,53 @@ def benchmark_grpo_logits_cuda(logits_new, logp_old, logp_ref, selected_tokens, 
         *_pf(x), *_pf(b), *_pf(c), *_pi(sel), *_pf(adv), *_pi(m), B, G, T, V, cfg.clip_eps, cfg.beta,
         int(cfg.reduction), cfg.length_alpha, warmup, iterations, C.byref(t0), C.byref(t1)))
     return CudaLogitsTiming(t0.value, t1.value)
+
+
+class ShardedLogits:
+    """One rank of a token-sharded batch: the host-facing call of ``grpo_b200_logits_sharded_host`` with
+    numpy metadata, the Python twin of ``grpo::ShardedLogitsBoundary``
+    (include/grpo/grpo_loss_sharded.hpp).  Argument meaning and errors follow
+    ``grpo_logits_cuda_device_inplace`` (include/grpo/grpo_loss_cuda.cuh:68-86 of the reference) for
+    this rank's rows ``[row_offset, row_offset + n_rows)``; the statistics returned are the whole
+    batch's.  Create with the rank's device current."""
+
+    def __init__(self, rank: int, world: int, B: int, G: int, T: int, V: int, P: int, row_offset: int, n_rows: int):
+        self.world = world
+        self._shard = C.c_void_p()
+        _lib.check(_lib.lib().grpo_b200_shard_create(rank, world, B * G, T, V, P, row_offset, n_rows,
+                                                    C.byref(self._shard)))
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        _lib.check(_lib.lib().grpo_b200_shard_export(self._shard, buf))
+        return buf.raw
+
+    def connect_ipc(self, handles) -> None:
+        """``handles``: every rank's 64 bytes, in rank order (processes, one per device)."""
+        if len(handles) != self.world:
+            raise ValueError("one handle per rank, in rank order")
+        flat = C.create_string_buffer(b"".join(bytes(h) for h in handles), 64 * self.world)
+        _lib.check(_lib.lib().grpo_b200_shard_connect_ipc(self._shard, flat))
+
+    def connect_local(self, all_shards) -> None:
+        """``all_shards``: every rank's object, in rank order (threads of one process)."""
+        arr = (C.c_void_p * self.world)(*[s._shard.value for s in all_shards])
+        _lib.check(_lib.lib().grpo_b200_shard_connect_local(self._shard, arr))
+
+    def run(self, logits_and_dlogits, logp_old, logp_ref, selected_tokens, advantages, mask,
+            config: LossConfig | None = None, kernel: CudaLogitsKernel = CudaLogitsKernel.fused) -> LossStats:
+        cfg = config or LossConfig()
+        b, c = _f32(logp_old), _f32(logp_ref)
+        sel, adv, m = _i32(selected_tokens), _f32(advantages), _i32(mask)
+        raw = np.zeros(3, np.float32)
+        valid = C.c_int(0)
+        _lib.check(_lib.lib().grpo_b200_logits_sharded_host(
+            self._shard, _device_pointer(logits_and_dlogits) or None, *_pf(b), *_pf(c), *_pi(sel), *_pf(adv), *_pi(m),
+            cfg.clip_eps, cfg.beta, int(cfg.reduction), cfg.length_alpha, int(kernel), raw.ctypes.data_as(_fp),
+            C.byref(valid)))
+        return _stats(raw, valid)
+
+    def close(self) -> None:
+        if self._shard:
+            _lib.lib().grpo_b200_shard_destroy(self._shard)
+            self._shard = C.c_void_p()

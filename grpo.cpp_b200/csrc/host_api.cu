@@ -19,9 +19,10 @@
 #include <vector>
 
 #include "common.cuh"
+#include "host_util.hpp"
 
 namespace grpo_b200 {
-namespace {
+namespace host {
 
 constexpr size_t kIntMaxSz = 2147483647u;
 
@@ -35,6 +36,10 @@ int nonfinite(const char* msg) {
     return GRPO_B200_E_NONFINITE;
 }
 
+}  // namespace host
+namespace {
+using namespace host;
+
 // ---- leased per-device buffers --------------------------------------------------------------
 struct Arena {
     int device = -1;
@@ -45,7 +50,13 @@ struct Arena {
     cudaEvent_t ev[2] = {nullptr, nullptr};
     unsigned* ticket = nullptr;  // zero between calls: the selected-token kernel's ticket counter
 
+    // On failure everything the arena holds is released, so the pool never keeps a half-built one.
     cudaError_t reserve(size_t dev_bytes, size_t pinned_bytes) {
+        const cudaError_t err = reserve_parts(dev_bytes, pinned_bytes);
+        if (err != cudaSuccess) release_memory();
+        return err;
+    }
+    cudaError_t reserve_parts(size_t dev_bytes, size_t pinned_bytes) {
         if (!ticket) {
             cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&ticket), 256);
             if (err != cudaSuccess) return err;
@@ -82,6 +93,10 @@ struct Arena {
         if (dev) cudaFree(dev);
         if (pinned) cudaFreeHost(pinned);
         if (ticket) cudaFree(ticket);
+        for (cudaEvent_t& e : ev) {
+            if (e) cudaEventDestroy(e);
+            e = nullptr;
+        }
         ticket = nullptr;
         dev = pinned = nullptr;
         dev_cap = pinned_cap = 0;
@@ -129,10 +144,9 @@ struct Bump {
 };
 size_t slice(size_t bytes) { return (bytes + 255) & ~static_cast<size_t>(255); }
 
+}  // namespace
+namespace host {
 // ---- validation (messages and order of src/cuda/grpo_loss_cuda.cu:584-618, 662-724) ----------
-struct Shape {
-    size_t sequences = 0, tokens = 0;
-};
 
 int checked_shape(int B, int G, int T, Shape& out) {
     // include/grpo/grpo_loss.hpp:51-67 of the reference
@@ -151,10 +165,6 @@ int expect_size(const char* name, size_t got, size_t want) {
     return invalid(std::string(name) + " has size " + std::to_string(got) + ", expected " + std::to_string(want));
 }
 
-struct Options {
-    float clip_eps, beta, alpha;
-    int reduction;
-};
 
 int check_options(const Options& o) {
     if (o.clip_eps < 0.0f || o.clip_eps >= 1.0f || !std::isfinite(o.clip_eps))
@@ -187,6 +197,8 @@ int validate_inputs(const float* lp_new, size_t n_new, const float* lp_old, size
     return GRPO_B200_OK;
 }
 
+}  // namespace host
+namespace {
 // Host twin of make_weights (src/cuda/grpo_loss_cuda.cu:21-57): same fp32 expressions.
 int make_weights(const int32_t* mask, const Shape& shape, int T, const Options& opt, float* weights,
                  int& valid_tokens) {
@@ -212,6 +224,8 @@ int make_weights(const int32_t* mask, const Shape& shape, int T, const Options& 
     return GRPO_B200_OK;
 }
 
+}  // namespace
+namespace host {
 int check_selected(const int32_t* selected, const int32_t* mask, size_t n, int V, size_t& first_bad) {
     first_bad = n;
     for (size_t i = 0; i < n; i++)
@@ -239,6 +253,8 @@ int fill_stats(const grpo_b200_result_t& r, float* stats, const char* what) {
     return GRPO_B200_OK;
 }
 
+}  // namespace host
+namespace {
 // Device image of the per-token metadata of a logits call, staged through one pinned block.
 struct LogitsMeta {
     float* old_d;
@@ -629,9 +645,11 @@ int grpo_b200_release_cache(void) {
     int device = 0;
     GRPO_CUDA_TRY(cudaGetDevice(&device));
     std::lock_guard<std::mutex> lock(g_pool_mutex);
-    for (Arena* a : g_pool[device]) {
+    for (Arena* a : g_pool[device]) {  // idle arenas only: a leased one is not in the pool
         a->release_memory();
+        delete a;
     }
+    g_pool[device].clear();
     return GRPO_B200_OK;
 }
 

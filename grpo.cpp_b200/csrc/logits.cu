@@ -340,8 +340,8 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     // and run its prologue; it still waits for this whole grid before it reads anything written here.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // The pass's control words start from zero without a separate clearing launch: block 0 is
-    // resident from the first instant (the grid never exceeds what fits at once), a wait gives up
-    // only after seconds, and the reduce kernel that reads them runs after this kernel.
+    // resident from the first instant (the grid never exceeds what fits at once), CTAs report into
+    // the status word only when they retire, and the reduce kernel that reads both runs after this kernel.
     if (blockIdx.x == 0 && tid == 0) {
         *a.status = 0;
         *a.counter = 0u;
@@ -1070,24 +1070,12 @@ struct Variant {
 
 // Capacity of a variant in floats: cluster * threads * vec * 4.  Name: cluster x threads x vec.
 constexpr Variant kVariants[] = {
-    {1, 512, 16, 4, 6, "1x512x16"},   // 0:  <=  32768  one CTA per SM, 192 KB ring of 32 KB stages
-    {2, 512, 16, 4, 6, "2x512x16"},   // 1:  <=  65536
-    {4, 512, 16, 4, 6, "4x512x16"},   // 2:  <= 131072
-    {8, 512, 16, 4, 6, "8x512x16"},   // 3:  <= 262144
-    {1, 256, 16, 4, 6, "1x256x16"},   // 4:  <=  16384  96 KB ring, two CTAs per SM
-    {2, 256, 16, 4, 6, "2x256x16"},   // 5:  <=  32768
-    {4, 256, 16, 4, 6, "4x256x16"},   // 6:  <=  65536
-    {8, 256, 16, 4, 6, "8x256x16"},   // 7:  <= 131072
-    {1, 512, 8, 2, 6, "1x512x8"},     // 8:  <=  16384  96 KB ring, two CTAs per SM, 64 registers
-    {2, 512, 8, 2, 6, "2x512x8"},     // 9:  <=  32768
-    {4, 512, 8, 2, 6, "4x512x8"},     // 10: <=  65536
-    {8, 512, 8, 2, 6, "8x512x8"},     // 11: <= 131072
-    {1, 512, 16, 2, 12, "1x512x16s"}, // 12: <=  32768  16 KB stages
-    {2, 512, 16, 2, 12, "2x512x16s"}, // 13: <=  65536
-    {1, 128, 16, 4, 6, "1x128x16"},   // 14: <=   8192  48 KB ring, four CTAs per SM
-    {2, 128, 16, 4, 6, "2x128x16"},   // 15: <=  16384
-    {4, 128, 16, 4, 6, "4x128x16"},   // 16: <=  32768
-    {8, 128, 16, 4, 6, "8x128x16"},   // 17: <=  65536
+    {1, 128, 16, 4, 6, "1x128x16"},   // 0: <=   8192   48 KB ring of 8 KB stages, four CTAs per SM
+    {2, 128, 16, 4, 6, "2x128x16"},   // 1: <=  16384
+    {4, 128, 16, 4, 6, "4x128x16"},   // 2: <=  32768
+    {8, 128, 16, 4, 6, "8x128x16"},   // 3: <=  65536   (GPT-2's 50,304)
+    {8, 256, 16, 4, 6, "8x256x16"},   // 4: <= 131072   96 KB ring, two CTAs per SM
+    {8, 512, 16, 4, 6, "8x512x16"},   // 5: <= 262144   192 KB ring of 32 KB stages, one CTA per SM
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -1144,24 +1132,12 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
 template <bool CHECK>
 cudaError_t launch_by_index(int variant, const LogitsArgs& a, cudaStream_t stream) {
     switch (variant) {
-        case 0: return launch_variant<512, 16, 4, 6, 1, CHECK>(a, stream);
-        case 1: return launch_variant<512, 16, 4, 6, 2, CHECK>(a, stream);
-        case 2: return launch_variant<512, 16, 4, 6, 4, CHECK>(a, stream);
-        case 3: return launch_variant<512, 16, 4, 6, 8, CHECK>(a, stream);
-        case 4: return launch_variant<256, 16, 4, 6, 1, CHECK>(a, stream);
-        case 5: return launch_variant<256, 16, 4, 6, 2, CHECK>(a, stream);
-        case 6: return launch_variant<256, 16, 4, 6, 4, CHECK>(a, stream);
-        case 7: return launch_variant<256, 16, 4, 6, 8, CHECK>(a, stream);
-        case 8: return launch_variant<512, 8, 2, 6, 1, CHECK>(a, stream);
-        case 9: return launch_variant<512, 8, 2, 6, 2, CHECK>(a, stream);
-        case 10: return launch_variant<512, 8, 2, 6, 4, CHECK>(a, stream);
-        case 11: return launch_variant<512, 8, 2, 6, 8, CHECK>(a, stream);
-        case 12: return launch_variant<512, 16, 2, 12, 1, CHECK>(a, stream);
-        case 13: return launch_variant<512, 16, 2, 12, 2, CHECK>(a, stream);
-        case 14: return launch_variant<128, 16, 4, 6, 1, CHECK>(a, stream);
-        case 15: return launch_variant<128, 16, 4, 6, 2, CHECK>(a, stream);
-        case 16: return launch_variant<128, 16, 4, 6, 4, CHECK>(a, stream);
-        case 17: return launch_variant<128, 16, 4, 6, 8, CHECK>(a, stream);
+        case 0: return launch_variant<128, 16, 4, 6, 1, CHECK>(a, stream);
+        case 1: return launch_variant<128, 16, 4, 6, 2, CHECK>(a, stream);
+        case 2: return launch_variant<128, 16, 4, 6, 4, CHECK>(a, stream);
+        case 3: return launch_variant<128, 16, 4, 6, 8, CHECK>(a, stream);
+        case 4: return launch_variant<256, 16, 4, 6, 8, CHECK>(a, stream);
+        case 5: return launch_variant<512, 16, 4, 6, 8, CHECK>(a, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -1200,8 +1176,7 @@ int pick_resident_variant(const void* logits, const void* dlogits, int V, int P,
     const int forced = g_forced_variant.load(std::memory_order_relaxed);
     if (forced >= 0 && forced < kNumVariants) return variant_fits(forced, P) ? forced : -1;
     // smallest CTAs whose cluster (at most 8) holds the row: four CTAs per SM overlap one another's serial phases
-    static const int order[] = {14, 15, 16, 17, 7, 3};
-    for (int idx : order)
+    for (int idx = 0; idx < kNumVariants; idx++)
         if (variant_fits(idx, P)) return idx;
     return -1;
 }

@@ -1,9 +1,12 @@
 // Public option and result types of the GRPO loss boundary, source-compatible with the
 // reference's include/grpo/grpo_loss.hpp (types at :10-43, shape guard at :46-67, index helpers at
-// :70-76) so that code written against the reference compiles unchanged against this library.
+// :70-76, CPU entry points at :78-117) so that code written against the reference compiles unchanged
+// against this header.
 //
-// This header declares data types only.  The reference's CPU functions (group_advantages_cpu,
-// grpo_loss_cpu, grpo_logits_cpu) are not part of this library: it has no CPU compute path.
+// The three CPU functions at the bottom are DECLARED here, with the reference's signatures, and
+// defined by the reference's own grpo_cpu library (src/cpu/grpo_loss.cpp), which a caller that uses
+// them keeps linking exactly as the reference's build does (CMakeLists.txt:46-48 links grpo_cpu into
+// grpo_cuda's users).  This library defines none of them: it has no CPU compute path.
 #pragma once
 
 #include <climits>
@@ -67,5 +70,16 @@ inline Shape checked_shape(int B, int G, int T) {
 // Row-major positions in the [B][G] and [B][G][T] layouts.
 inline std::size_t idx2(int b, int g, int G) { return static_cast<std::size_t>(b) * G + g; }
 inline std::size_t idx3(int b, int g, int t, int G, int T) { return idx2(b, g, G) * T + t; }
+
+// Defined by the reference's grpo_cpu library, not by this one (see the note at the top).
+std::vector<float> group_advantages_cpu(const std::vector<float>& rewards, int B, int G,
+                                        AdvantageMode mode = AdvantageMode::standardized, float eps = 1e-8f);
+LossResult grpo_loss_cpu(const std::vector<float>& logp_new, const std::vector<float>& logp_old,
+                         const std::vector<float>& logp_ref, const std::vector<float>& advantages,
+                         const std::vector<int>& mask, int B, int G, int T, LossConfig config = {});
+LogitsLossResult grpo_logits_cpu(const std::vector<float>& logits_new, const std::vector<float>& logp_old,
+                                 const std::vector<float>& logp_ref, const std::vector<int>& selected_tokens,
+                                 const std::vector<float>& advantages, const std::vector<int>& mask, int B, int G,
+                                 int T, int V, LossConfig config = {});
 
 }  // namespace grpo

@@ -370,6 +370,48 @@ int grpo_b200_benchmark_logits_host(const float* logits, size_t n_logits, const 
                                     float clip_eps, float beta, int reduction, float length_alpha,
                                     int warmup, int iterations, float* separate_ms, float* fused_ms);
 
+/* Token-sharded run, host side: grpo_logits_cuda_device_inplace (include/grpo/grpo_loss_cuda.cuh:68-86,
+ * src/cuda/grpo_loss_cuda.cu:774-817) for ONE RANK'S ROWS of a batch whose rows are spread over up to
+ * eight GPUs of one box, for the reference's two kinds of multi-GPU caller: one host thread per device
+ * in one process (apps/03_two_gpu_train.cu:200-215) and one process per device
+ * (apps/05_two_gpu_gpt2_grpo.cu:309-328).
+ *
+ * A shard owns what one rank needs between calls: its exchange region, device copies of the per-token
+ * metadata, pinned staging, workspace.  grpo_b200_shard_create is called with the rank's device current
+ * (rows [row_offset, row_offset + n_rows) of a batch of n_seq responses of tokens_per_seq slots).  Then
+ * the ranks connect, either way:
+ *   processes: every rank exports 64 bytes (grpo_b200_shard_export), the ranks trade them by whatever
+ *              channel they have, and each calls grpo_b200_shard_connect_ipc with all world handles
+ *              concatenated in rank order (its own entry is ignored);
+ *   threads:   every rank calls grpo_b200_shard_connect_local with the array of all world shards in rank
+ *              order (peer access between the devices is enabled as needed), after all were created.
+ * The ranks line up on the host (a barrier) after connecting and before every call on a new batch.
+ *
+ * grpo_b200_logits_sharded_host: this rank's host metadata in (logp_old, logp_ref, selected, mask:
+ * n_rows entries each; advantages: all n_seq), this rank's device logits (n_rows x P) replaced in place
+ * by dL/dlogits, and the GLOBAL loss, pg_loss, kl and valid-token count out -- the same on every rank,
+ * bit for bit.  One packed pinned upload, the lengths exchange, the row order, the row kernel and the
+ * reduce kernel (with the record exchange over NVLink peer memory) enqueued on the legacy default stream
+ * without an intermediate synchronisation, one pinned read-back; returns after the device work is
+ * complete.  Errors as the reference's call, applied to the global quantities ("every sequence needs at
+ * least one valid token" looks at the whole batch); a rank whose peers do not answer within the exchange
+ * timeout gets GRPO_B200_E_CUDA "the exchange between ranks timed out".  Every rank makes the same
+ * sequence of calls; a rank that returns early on an argument error leaves its peers to that timeout. */
+typedef struct grpo_b200_shard* grpo_b200_shard_t;
+int grpo_b200_shard_create(int rank, int world, int64_t n_seq, int tokens_per_seq, int V, int P,
+                           int64_t row_offset, int64_t n_rows, grpo_b200_shard_t* shard);
+int grpo_b200_shard_export(grpo_b200_shard_t shard, unsigned char handle[64]);
+int grpo_b200_shard_connect_ipc(grpo_b200_shard_t shard, const unsigned char* handles);
+int grpo_b200_shard_connect_local(grpo_b200_shard_t shard, grpo_b200_shard_t const* all_shards);
+int grpo_b200_shard_destroy(grpo_b200_shard_t shard);
+int grpo_b200_logits_sharded_host(grpo_b200_shard_t shard, float* logits_and_dlogits,
+                                  const float* logp_old, size_t n_logp_old, const float* logp_ref,
+                                  size_t n_logp_ref, const int32_t* selected, size_t n_selected,
+                                  const float* advantages, size_t n_advantages, const int32_t* mask,
+                                  size_t n_mask, float clip_eps, float beta, int reduction,
+                                  float length_alpha, int kernel, float* stats_out,
+                                  int* valid_tokens_out);
+
 /* Frees the calling thread's current device's cached workspace and staging buffers. */
 int grpo_b200_release_cache(void);
 

@@ -382,7 +382,7 @@ def test_row_order_partition_and_invariance():
         assert (got == want).all()
     names = D.variants()
     try:
-        for name, V, min_len in (("1x128x16", 1000, 1), ("4x128x16", 30000, 3), ("8x128x16", 50257, 1), ("2x512x16", 40000, 12)):
+        for name, V, min_len in (("1x128x16", 1000, 1), ("4x128x16", 30000, 3), ("8x128x16", 50257, 1), ("8x256x16", 40000, 12)):
             P = (V + 3) // 4 * 4 + 8
             b = W.logits_case(3, 4, 12, V, sigma=2.0, min_len=min_len, reduction=W.TOKEN_MEAN, seed=len(name) + V)
             t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
