@@ -730,6 +730,84 @@ def gpu_arm(args, spec: dict) -> None:
     print(json.dumps(line), flush=True)
 
 
+def gradsync_arm(args) -> None:
+    """`--workload gradsync`: the in-place sum of one 124,439,808-float gradient buffer per rank times
+    1/world -- GPT-2 124M's parameter count, what the reference's two-GPU demo all-reduces and then scales
+    (apps/05_two_gpu_gpt2_grpo.cu:216-219, 260-268) -- by the library's one kernel over NVLink peer memory,
+    next to ncclAllReduce followed by a scale kernel on the same GPUs.  One JSON line from rank 0."""
+    import torch
+    import torch.distributed as dist
+    from grpo_cpp_b200 import device as D
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    n = 124_439_808
+    g = torch.empty(n, device=dev)
+    src = torch.empty(n, device=dev).normal_(0.0, 1.0, generator=torch.Generator(device=dev).manual_seed(7 + rank))
+    sync = D.GradSync(g, rank, world)
+    handles = [None] * world
+    if world > 1:
+        dist.all_gather_object(handles, sync.handle)
+    else:
+        handles[0] = sync.handle
+    sync.connect(handles)
+    align = torch.zeros(1, device=dev)
+    scale = 1.0 / world
+
+    def timed(fn, passes):
+        pairs = []
+        for i in range(3 + passes):
+            g.copy_(src)
+            if world > 1:
+                dist.all_reduce(align)  # lines the ranks up, outside the event pair
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            if i >= 3:
+                pairs.append((e0, e1))
+        torch.cuda.synchronize()
+        t = torch.tensor([statistics.median(a.elapsed_time(b) for a, b in pairs)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def nccl_then_scale():
+        if world > 1:
+            dist.all_reduce(g)
+        g.mul_(scale)
+
+    ours_ms = timed(lambda: sync.allreduce_scale(scale), args.steps)
+    ours = g.clone()
+    nccl_ms = timed(nccl_then_scale, args.steps)
+    same = bool(torch.equal(ours, g)) if world <= 2 else None  # beyond two ranks NCCL's order of additions is its own
+    max_diff = float((ours - g).abs().max().item())
+    timed_out = sync.timed_out()
+    if world > 1:
+        dist.barrier()
+    sync.close()
+    if rank == 0:
+        link_bytes = 4 * n * (world - 1) / world  # per rank and direction: the other ranks' shares of its slice in, its results out
+        print(json.dumps({
+            "metric": "gradient all-reduce + 1/world scale, ms per call", "workload": "gradsync", "n_gpus": world,
+            "floats": n, "steps": args.steps, "fused_kernel_ms": ours_ms, "nccl_allreduce_plus_scale_ms": nccl_ms,
+            "speedup_vs_nccl_plus_scale": nccl_ms / ours_ms if ours_ms else None,
+            "nvlink_bytes_per_rank_per_direction": link_bytes,
+            "nvlink_gbs_per_direction": link_bytes / (ours_ms * 1e-3) / 1e9 if world > 1 else None,
+            "nvlink_roofline": {"peak_gbs_per_direction": 770.0, "frac": (link_bytes / (ours_ms * 1e-3) / 1e9 / 770.0) if world > 1 else None,
+                                "note": "measured peer-copy bandwidth of this pool; nominal 900"},
+            "hbm_gbs_at_one_rank": (2 * 4 * n / (ours_ms * 1e-3) / 1e9) if world == 1 else None,
+            "bit_identical_to_nccl_plus_scale": same, "max_abs_diff_vs_nccl_plus_scale": max_diff,
+            "timed_out": timed_out}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu
 # capture, scaled to the full launch where a smaller case was captured (see profiles/); null
 # until a capture exists for that workload.
@@ -748,8 +826,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     tune = ap.add_argument_group("tuning and profiling (not used by the default run)")
-    tune.add_argument("--workload", default="gpt2", choices=["gpt2", "v32k", "v128k_a0.5", "v128k_a1.0"],
-                      help="which configuration the headline line measures")
+    tune.add_argument("--workload", default="gpt2", choices=["gpt2", "v32k", "v128k_a0.5", "v128k_a1.0", "gradsync"],
+                      help="which configuration the headline line measures; gradsync: the fused gradient "
+                           "all-reduce + scale kernel against NCCL + scale (a line of its own)")
     tune.add_argument("--prompts", type=int, default=None,
                       help="override the workload's number of prompts B (rows = B x G x T): the same row shape at "
                            "another batch size, e.g. a few thousand rows for a multi-pass profiler capture")
@@ -762,6 +841,10 @@ def main() -> None:
     tune.add_argument("--no-graph", action="store_true", help="launch each pass eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     import grpo_cpp_b200  # noqa: F401  (registers the package under its importable name)
+    if args.workload == "gradsync":
+        if args.impl == "b200":
+            gradsync_arm(args)
+        return
     spec = workload_spec(args.workload)
     if args.prompts is not None:
         spec["B"] = args.prompts

@@ -77,6 +77,15 @@ SIGNATURES = {
     "grpo_b200_shard_destroy": (_int, [_vp]),
     "grpo_b200_logits_sharded_host": (_int, [_vp, _vp, _f, _sz, _f, _sz, _i, _sz, _f, _sz, _i, _sz, _flt, _flt, _int,
                                              _flt, _int, _f, C.POINTER(_int)]),
+    "grpo_b200_gradsync_slice": (None, [_i64, _int, _int, C.POINTER(_i64), C.POINTER(_i64)]),
+    "grpo_b200_gradsync_create": (_int, [_int, _int, _vp, _i64, C.POINTER(_vp)]),
+    "grpo_b200_gradsync_export": (_int, [_vp, C.c_char_p]),
+    "grpo_b200_gradsync_connect_ipc": (_int, [_vp, C.c_char_p]),
+    "grpo_b200_gradsync_connect_local": (_int, [_vp, C.POINTER(_vp)]),
+    "grpo_b200_gradsync_set_timeout_cycles": (_int, [_i64]),
+    "grpo_b200_allreduce_scale": (_int, [_vp, _flt, _vp]),
+    "grpo_b200_gradsync_status": (_int, [_vp, C.POINTER(_int)]),
+    "grpo_b200_gradsync_destroy": (_int, [_vp]),
     "grpo_b200_release_cache": (_int, []),
 }
 

@@ -364,3 +364,52 @@ class ResidentBoundary:
         weights_from_lengths(self.lengths, self.reduction, self.alpha, self.weights, self.meta)
         return logits(logits_t, logp_old, logp_ref, selected, advantages, self.weights, mask, self.T, self.V,
                       self.clip_eps, self.beta, kernel=kernel, result=self.result, workspace=self.workspace)
+
+
+def gradsync_slice(n: int, world: int, rank: int) -> tuple[int, int]:
+    """``(first, count)`` in floats of the slice rank ``rank`` reduces in :class:`GradSync` (the
+    library's own arithmetic: whole float4s, the last rank takes the tail).  Needs no device."""
+    import ctypes as C
+    first, count = C.c_int64(), C.c_int64()
+    _lib.lib().grpo_b200_gradsync_slice(n, world, rank, C.byref(first), C.byref(count))
+    return first.value, count.value
+
+
+class GradSync:
+    """In-place sum of one fp32 buffer per rank times ``scale``, by the library's own kernel over
+    NVLink peer memory (``grpo_b200_allreduce_scale``): what the reference's two-GPU GPT-2 demo does
+    with ncclAllReduce followed by scale_kernel (apps/05_two_gpu_gpt2_grpo.cu:216-219, 260-268).
+    ``grads`` is this rank's flat fp32 CUDA tensor; every rank registers a buffer of the same size,
+    the ranks trade :attr:`handle` (192 bytes) and call :meth:`connect`."""
+
+    def __init__(self, grads: torch.Tensor, rank: int, world: int):
+        import ctypes as C
+        self.grads, self.rank, self.world = grads, rank, world
+        self._h = C.c_void_p()
+        _lib.check(_lib.lib().grpo_b200_gradsync_create(rank, world, _check_tensor(grads, torch.float32, "grads"),
+                                                       grads.numel(), C.byref(self._h)))
+        buf = C.create_string_buffer(192)
+        _lib.check(_lib.lib().grpo_b200_gradsync_export(self._h, buf))
+        self.handle = buf.raw
+
+    def connect(self, handles) -> None:
+        import ctypes as C
+        if len(handles) != self.world:
+            raise ValueError("one handle per rank, in rank order")
+        flat = C.create_string_buffer(b"".join(bytes(h) for h in handles), 192 * self.world)
+        _lib.check(_lib.lib().grpo_b200_gradsync_connect_ipc(self._h, flat))
+
+    def allreduce_scale(self, scale: float) -> None:
+        """Enqueues the kernel on the current stream; every rank makes the same calls."""
+        _lib.check(_lib.lib().grpo_b200_allreduce_scale(self._h, float(scale), _stream()))
+
+    def timed_out(self) -> bool:
+        import ctypes as C
+        flag = C.c_int(0)
+        _lib.check(_lib.lib().grpo_b200_gradsync_status(self._h, C.byref(flag)))
+        return flag.value != 0
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().grpo_b200_gradsync_destroy(self._h)
+            self._h = None

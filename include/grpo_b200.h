@@ -412,6 +412,35 @@ int grpo_b200_logits_sharded_host(grpo_b200_shard_t shard, float* logits_and_dlo
                                   float length_alpha, int kernel, float* stats_out,
                                   int* valid_tokens_out);
 
+/* Gradient all-reduce fused with the 1/world scale, in place, by ONE kernel per rank over NVLink peer
+ * memory.  Replaces ncclAllReduce(grads) followed by scale_kernel(grads, 1/world) of the reference's
+ * two-GPU GPT-2 demo (apps/05_two_gpu_gpt2_grpo.cu:216-219, 260-268), which moves the data through a
+ * collective and then reads and writes all of it again.  Rank r loads slice r of every rank's buffer
+ * (peer loads), adds the terms in rank order, multiplies by `scale`, and stores the result into slice r
+ * of every rank's buffer (peer stores): every replica ends with the same bits, as the demo's replica
+ * hash check requires (:330-342).
+ *
+ * A handle registers this rank's buffer (device memory, 16-byte aligned, n floats; it may lie inside a
+ * larger allocation) with the rank's device current.  Ranks connect like shards do: processes trade the
+ * 192-byte blocks of grpo_b200_gradsync_export and call _connect_ipc with all of them concatenated in
+ * rank order; threads of one process call _connect_local with all handles in rank order.  After that,
+ * every rank calls grpo_b200_allreduce_scale the same number of times; the call only enqueues the
+ * kernel.  The ranks' kernels wait for one another through flag words (bounded: about four seconds of SM
+ * clock unless grpo_b200_gradsync_set_timeout_cycles changed it); grpo_b200_gradsync_status reads back
+ * whether a wait on this rank ever gave up (it synchronises the device).
+ * grpo_b200_gradsync_slice is the slice arithmetic itself (pure host code): floats
+ * [first, first + count) are what rank `rank` reduces; whole float4s, the last rank taking the tail. */
+typedef struct grpo_b200_gradsync* grpo_b200_gradsync_t;
+void grpo_b200_gradsync_slice(int64_t n, int world, int rank, int64_t* first, int64_t* count);
+int grpo_b200_gradsync_create(int rank, int world, float* grads, int64_t n, grpo_b200_gradsync_t* handle);
+int grpo_b200_gradsync_export(grpo_b200_gradsync_t handle, unsigned char block[192]);
+int grpo_b200_gradsync_connect_ipc(grpo_b200_gradsync_t handle, const unsigned char* blocks);
+int grpo_b200_gradsync_connect_local(grpo_b200_gradsync_t handle, grpo_b200_gradsync_t const* all_handles);
+int grpo_b200_gradsync_set_timeout_cycles(int64_t cycles);
+int grpo_b200_allreduce_scale(grpo_b200_gradsync_t handle, float scale, grpo_b200_stream_t stream);
+int grpo_b200_gradsync_status(grpo_b200_gradsync_t handle, int* timed_out);
+int grpo_b200_gradsync_destroy(grpo_b200_gradsync_t handle);
+
 /* Frees the calling thread's current device's cached workspace and staging buffers. */
 int grpo_b200_release_cache(void);
 
