@@ -792,7 +792,7 @@ def gradsync_arm(args) -> None:
         dist.barrier()
     sync.close()
     if rank == 0:
-        link_bytes = 4 * n * (world - 1) / world  # per rank and direction: the other ranks' shares of its slice in, its results out
+        link_bytes = 2 * 4 * n * (world - 1) / world  # per rank and direction: in, the peers' terms of its slice and their results; out, the mirror image
         print(json.dumps({
             "metric": "gradient all-reduce + 1/world scale, ms per call", "workload": "gradsync", "n_gpus": world,
             "floats": n, "steps": args.steps, "fused_kernel_ms": ours_ms, "nccl_allreduce_plus_scale_ms": nccl_ms,

@@ -86,6 +86,9 @@ SIGNATURES = {
     "grpo_b200_allreduce_scale": (_int, [_vp, _flt, _vp]),
     "grpo_b200_gradsync_status": (_int, [_vp, C.POINTER(_int)]),
     "grpo_b200_gradsync_destroy": (_int, [_vp]),
+    "grpo_b200_lmhead_workspace_bytes": (_sz, [_i64, _int]),
+    "grpo_b200_lmhead_loss": (_int, [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _flt,
+                                     _flt, _vp, _vp, _vp, _vp, _sz, _vp]),
     "grpo_b200_release_cache": (_int, []),
 }
 

@@ -27,7 +27,7 @@ namespace {
 
 constexpr int kMaxWorld = 8;
 constexpr int kSyncThreads = 512;
-constexpr int kUnroll = 2;  // float4 per thread per step
+constexpr int kUnroll = 4;  // float4 per thread per step
 
 struct SyncFlags {                                 // one per rank, in device memory every rank maps
     unsigned long long arrived[kMaxWorld];        // [source rank]: the epoch of its last "gradients final"
@@ -54,6 +54,7 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// system-scope accesses: the data was written by (and goes to) other GPUs
 __device__ __forceinline__ float4 ld_peer(const float4* p) {
     float4 v;
     asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
@@ -93,18 +94,20 @@ __global__ void __launch_bounds__(kSyncThreads) allreduce_scale_kernel(const Syn
         const long long per = (n4 + WORLD - 1) / WORLD;
         const long long first = min(static_cast<long long>(a.rank) * per, n4);
         const long long count = min(first + per, n4) - first;
-        const long long stride = static_cast<long long>(gridDim.x) * kSyncThreads * kUnroll;
-        for (long long i = (static_cast<long long>(blockIdx.x) * kSyncThreads + tid) * kUnroll; i < count; i += stride) {
+        // consecutive lanes take consecutive float4s (every load and store instruction of a warp covers 512
+        // contiguous bytes); a thread's kUnroll elements lie a whole grid apart
+        const long long lanes = static_cast<long long>(gridDim.x) * kSyncThreads;
+        for (long long i0 = static_cast<long long>(blockIdx.x) * kSyncThreads + tid; i0 < count; i0 += lanes * kUnroll) {
             float4 acc[kUnroll];
             float4 term[kUnroll][WORLD];
 #pragma unroll
             for (int u = 0; u < kUnroll; u++)
 #pragma unroll
                 for (int q = 0; q < WORLD; q++)
-                    if (i + u < count) term[u][q] = ld_peer(reinterpret_cast<const float4*>(a.bufs[q]) + first + i + u);
+                    if (i0 + u * lanes < count) term[u][q] = ld_peer(reinterpret_cast<const float4*>(a.bufs[q]) + first + i0 + u * lanes);
 #pragma unroll
             for (int u = 0; u < kUnroll; u++) {
-                if (i + u >= count) continue;
+                if (i0 + u * lanes >= count) continue;
                 acc[u] = term[u][0];
 #pragma unroll
                 for (int q = 1; q < WORLD; q++) {  // rank order: the same bits on every replica
@@ -118,7 +121,7 @@ __global__ void __launch_bounds__(kSyncThreads) allreduce_scale_kernel(const Syn
                 acc[u].z = __fmul_rn(acc[u].z, a.scale);
                 acc[u].w = __fmul_rn(acc[u].w, a.scale);
 #pragma unroll
-                for (int q = 0; q < WORLD; q++) st_peer(reinterpret_cast<float4*>(a.bufs[q]) + first + i + u, acc[u]);
+                for (int q = 0; q < WORLD; q++) st_peer(reinterpret_cast<float4*>(a.bufs[q]) + first + i0 + u * lanes, acc[u]);
             }
         }
         if (a.rank == WORLD - 1) {  // the up-to-three floats past the last whole float4
@@ -341,7 +344,7 @@ int grpo_b200_allreduce_scale(grpo_b200_gradsync_t h, float scale, grpo_b200_str
     const long long n4 = h->n >> 2;
     const long long per = (n4 + h->world - 1) / h->world;
     long long blocks = (per + kSyncThreads * kUnroll - 1) / (kSyncThreads * kUnroll);
-    const long long cap = static_cast<long long>(h->sms) * 2;  // (no CTA waits for another: the grid need not be resident at once)
+    const long long cap = static_cast<long long>(h->sms) * 2;  // (no CTA waits for another CTA: the grid need not be resident at once)  // (no CTA waits for another: the grid need not be resident at once)
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -413,3 +413,28 @@ class GradSync:
         if self._h:
             _lib.lib().grpo_b200_gradsync_destroy(self._h)
             self._h = None
+
+
+def lmhead_loss(hidden: torch.Tensor, lm_head: torch.Tensor, V: int, logp_old, logp_ref, selected, advantages, weights,
+                mask, tokens_per_seq: int, clip_eps: float, beta: float, *, row_offset: int = 0,
+                want_selected_logp: bool = False, want_lse: bool = False):
+    """LM-head projection fused with the loss statistics (``grpo_b200_lmhead_loss``): ``hidden`` is
+    ``[n_rows, C]`` and ``lm_head`` ``[P, C]`` fp32 (read as TF32 by the tensor cores); the logits are
+    never materialised.  Returns ``(result, selected_logp or None, lse or None)``."""
+    n_rows, C = hidden.shape
+    P = lm_head.shape[0]
+    if lm_head.shape[1] != C:
+        raise ValueError("hidden and lm_head must share the inner dimension")
+    dev = hidden.device
+    result = new_result(dev)
+    ws = torch.empty(_lib.lib().grpo_b200_lmhead_workspace_bytes(n_rows, P), dtype=torch.uint8, device=dev)
+    lp = torch.empty(n_rows, dtype=torch.float32, device=dev) if want_selected_logp else None
+    lse = torch.empty(n_rows, dtype=torch.float64, device=dev) if want_lse else None
+    _lib.check(_lib.lib().grpo_b200_lmhead_loss(
+        _check_tensor(hidden, torch.float32, "hidden"), _check_tensor(lm_head, torch.float32, "lm_head"), n_rows, C, V, P,
+        _check_tensor(logp_old, torch.float32, "logp_old"), _check_tensor(logp_ref, torch.float32, "logp_ref"),
+        _check_tensor(selected, torch.int32, "selected"), _check_tensor(advantages, torch.float32, "advantages"),
+        _check_tensor(weights, torch.float32, "weights"), _check_tensor(mask, torch.int32, "mask"), row_offset,
+        tokens_per_seq, float(clip_eps), float(beta), None if lp is None else lp.data_ptr(),
+        None if lse is None else lse.data_ptr(), result.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
+    return result, lp, lse

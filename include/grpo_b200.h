@@ -441,6 +441,27 @@ int grpo_b200_allreduce_scale(grpo_b200_gradsync_t handle, float scale, grpo_b20
 int grpo_b200_gradsync_status(grpo_b200_gradsync_t handle, int* timed_out);
 int grpo_b200_gradsync_destroy(grpo_b200_gradsync_t handle);
 
+/* LM-head projection fused with the loss statistics (forward): logits = hidden[n_rows][C] x
+ * lm_head[P][C]^T are formed tile by tile on the tensor cores (tcgen05.mma, TF32 inputs, fp32
+ * accumulation in tensor memory) and reduced at once to the row maximum, the normaliser and the selected
+ * logit; the [n_rows][P] logits are never written.  Then the logits path's reduce kernel turns the row
+ * records into the three weighted sums.  Stands where the reference runs gpt2_forward's last matmul into
+ * model.acts.output and hands the N x P logits to the loss (apps/04_gpt2_grpo.cu:322-331); it gives the
+ * loss terms and log p(selected), not the gradient (that half would recompute the tiles).
+ * hidden and lm_head: device, fp32, row-major, 16-byte aligned, C a multiple of 32; rows [V, P) of
+ * lm_head are never used.  The tensor cores read fp32 words as TF32 (the low 13 mantissa bits are
+ * ignored), the precision of the TF32 matmul llm.c uses for this projection.  selected_logp[n_rows]
+ * (nullable) receives log p(selected) (0 for masked rows), lse_out[n_rows] (nullable) the row
+ * log-sum-exp.  Everything else as grpo_b200_logits; the workspace is larger
+ * (grpo_b200_lmhead_workspace_bytes).  Single-GPU code: one CTA per SM, no cluster, no multicast. */
+size_t grpo_b200_lmhead_workspace_bytes(int64_t n_rows, int P);
+int grpo_b200_lmhead_loss(const float* hidden, const float* lm_head, int64_t n_rows, int C, int V, int P,
+                          const float* logp_old, const float* logp_ref, const int32_t* selected,
+                          const float* advantages, const float* weights, const int32_t* mask,
+                          int64_t row_offset, int tokens_per_seq, float clip_eps, float beta,
+                          float* selected_logp, double* lse_out, grpo_b200_result_t* result,
+                          void* workspace, size_t workspace_bytes, grpo_b200_stream_t stream);
+
 /* Frees the calling thread's current device's cached workspace and staging buffers. */
 int grpo_b200_release_cache(void);
 
