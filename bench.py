@@ -468,6 +468,67 @@ def other_token_config(tokens_per_seq: int, ragged: bool, dev, flush, peak: floa
             "l2": "flushed between passes"}
 
 
+def lmhead_config(dev, flush, passes: int = 12) -> dict:
+    """The LM-head projection fused with the loss statistics on 4,096 GPT-2-shaped rows (hidden 768,
+    V = 50,257 padded to 50,304): tcgen05 tensor cores, TF32 inputs, fp32 accumulation, no logits
+    written.  Beside it, on the same inputs: a cuBLAS TF32 matmul that writes the 824 MB of logits
+    (torch.matmul, a library kernel: the baseline) followed by this library's fused logits pass."""
+    import torch
+    from grpo_cpp_b200 import device as D, workloads as W
+    n_seq, T, C, V, P = 16, 256, 768, 50257, 50304
+    N = n_seq * T
+    rng = np.random.Generator(np.random.PCG64(11))
+    gen = torch.Generator(device=dev).manual_seed(11)
+    hidden = torch.empty(N, C, device=dev).normal_(0.0, 1.0, generator=gen)
+    lm_head = torch.empty(P, C, device=dev).normal_(0.0, 3.0 / C ** 0.5, generator=gen)
+    mask_h = W.prefix_mask(rng.integers(32, T + 1, n_seq), T)
+    sel_h = np.where(mask_h == 1, rng.integers(0, V, N), -1).astype(np.int32)
+    adv_h = W.group_advantages_np((rng.random(n_seq) < 0.5).astype(np.float32), n_seq // 8, 8)
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    mask, sel, adv = to(mask_h), to(sel_h), to(adv_h)
+    weights, _ = D.weights_from_lengths(D.count_lengths(mask, n_seq, T), W.TOKEN_MEAN, 0.0)
+    old = torch.full((N,), -11.5, device=dev)
+    ref = torch.full((N,), -11.4, device=dev)
+    med, mean, best = time_passes(lambda: D.lmhead_loss(hidden, lm_head, V, old, ref, sel, adv, weights, mask, T, CLIP_EPS, BETA),
+                                  lambda: flush(), passes)
+    fused_rec = D.lmhead_loss(hidden, lm_head, V, old, ref, sel, adv, weights, mask, T, CLIP_EPS, BETA)[0].cpu().tolist()
+    logits = torch.empty(N, P, device=dev)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    result, ws, order = D.new_result(dev), D.logits_workspace(N, dev), D.row_order(mask)
+
+    def unfused():
+        torch.matmul(hidden, lm_head.T, out=logits)
+        D.logits(logits, old, ref, sel, adv, weights, mask, T, V, CLIP_EPS, BETA, result=result, workspace=ws,
+                 row_order=order)
+
+    try:
+        gemm_med, _, _ = time_passes(lambda: torch.matmul(hidden, lm_head.T, out=logits), lambda: flush(), passes)
+        unf_med, _, _ = time_passes(unfused, lambda: flush(), passes)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    unf_rec = result.cpu().tolist()
+    flops = 2.0 * N * P * C
+    peak_bf16 = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_bf16 = float(json.load(f)["bf16_tflops"])
+    except (OSError, KeyError, ValueError):
+        peak_bf16 = 1590.0
+    peak_tf32 = peak_bf16 / 2.0
+    return {"workload": f"LM-head fused with loss statistics, {N} rows x V={V} (P={P}) x C={C}, TF32 in / fp32 accumulate",
+            "passes": passes, "ms_per_pass": med, "ms_per_pass_min": best, "tokens_per_s": N / (med * 1e-3),
+            "launches_per_pass": 3,
+            "roofline": {"bound": "tensor", "flops": flops, "achieved": flops / med / 1e9, "unit": "TFLOP/s",
+                         "peak": peak_tf32, "frac": flops / med / 1e9 / peak_tf32,
+                         "peak_source": "half of the measured dense bf16 cuBLAS burst figure (TF32 runs at half the bf16 rate)"},
+            "cublas_tf32_matmul_writing_logits_ms": gemm_med,
+            "cublas_tf32_matmul_tflops": flops / gemm_med / 1e9,
+            "cublas_matmul_then_fused_logits_pass_ms": unf_med,
+            "loss_fused": fused_rec[0], "loss_matmul_then_logits_pass": unf_rec[0],
+            "logits_bytes_not_written": 4 * N * P, "l2": "flushed between passes"}
+
+
 def same_protocol_leg(dev) -> dict:
     """This library under the reference's own timing protocol (its benchmark entry points, which
     this library exports with the same signatures), for a like-for-like line beside
@@ -722,6 +783,7 @@ def gpu_arm(args, spec: dict) -> None:
         for name, T2, ragged in (("cfg2_1M", 256, False), ("cfg2_1M_ragged", 256, True), ("cfg2_4M", 1024, False),
                                  ("cfg2_4M_ragged", 1024, True)):
             others[name] = other_token_config(T2, ragged, dev, flush, peak)
+        others["lmhead_4096"] = lmhead_config(dev, flush)
         line["other_configs"] = others
         line["reference_cuda"] = reference_cuda_leg(["v32k", "v128k_a0.5", "v128k_a1.0", "cfg2_1M", "cfg2_4M"])
         line["same_protocol_as_reference_cuda"] = same_protocol_leg(dev)

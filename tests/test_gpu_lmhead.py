@@ -5,9 +5,11 @@ Checker: the inputs are rounded to TF32 on the host (low 13 mantissa bits cleare
 cores' own rounding of the inputs is a no-op and every product is exact; the host forms the logits of
 the checked rows in float64 and feeds their float64 log-softmax, rounded to fp32 as the reference
 rounds it, to the CPU checker's token loss.  What remains is the order of the fp32 accumulation over
-the 768 products of a logit (about 1e-6 relative per logit) and the fp32 running sum of exponentials.
-Tolerances, written below: row log-sum-exp and log p(selected) within 2e-5 absolute; the three loss
-sums within 2e-4 relative (they are cancelling sums of terms that each move by ~1e-5).
+the 768 products of a logit and the fp32 running sum of exponentials.  The tensor cores truncate
+when they accumulate, so a logit of magnitude ~10 comes out up to ~2e-5 towards zero and the row
+log-sum-exp reads 1e-5 to 2.5e-5 low at C = 768 (measured; far less at small C) -- the same holds for
+any tensor-core matmul of this precision.  Tolerances, written below: row log-sum-exp and
+log p(selected) within 5e-5 absolute; the three loss sums within 1e-4 relative (measured: 2e-5).
 """
 import numpy as np
 import pytest
@@ -62,17 +64,17 @@ def test_fused_projection_matches_the_host_in_float64(n_seq, T, C, V, P):
     rec = res.cpu().numpy()
     assert rec[3] == 0 and rec[4] == 0, rec
     active = mask == 1
-    assert np.abs(got_lse.cpu().numpy()[active] - lse[active]).max() <= 2e-5
-    assert np.abs(lp.cpu().numpy()[active] - now[active]).max() <= 2e-5
+    assert np.abs(got_lse.cpu().numpy()[active] - lse[active]).max() <= 5e-5
+    assert np.abs(lp.cpu().numpy()[active] - now[active]).max() <= 5e-5
     assert (lp.cpu().numpy()[~active] == 0).all()
-    assert (np.abs(rec[:3] - want[0]) <= 2e-4 * np.abs(want[0]) + 1e-7).all(), (rec[:3], want[0])
+    assert (np.abs(rec[:3] - want[0]) <= 1e-4 * np.abs(want[0]) + 1e-7).all(), (rec[:3], want[0])
     assert meta.cpu().tolist()[0] == want[1]
 
 
 def test_fused_projection_against_the_materialised_path_at_gpt2_size():
     """4,096 rows x V = 50,257 x C = 768: the same batch through (a) an fp32 matmul that writes the 824 MB
     of logits followed by the fused logits kernel, and (b) the fused projection, which writes none; the
-    three sums agree within 2e-4 relative, log p(selected) within 2e-5, and 64 rows are checked against
+    three sums agree within 1e-4 relative, log p(selected) within 5e-5, and 64 rows are checked against
     the host in float64."""
     import torch
     from grpo_cpp_b200 import device as D
@@ -101,12 +103,12 @@ def test_fused_projection_against_the_materialised_path_at_gpt2_size():
                                      want_selected_logp=True, want_lse=True)
     rec_b = res.cpu().numpy()
     assert rec_b[3] == 0 and rec_b[4] == 0
-    assert (np.abs(rec_b[:3] - rec_a[:3]) <= 2e-4 * np.abs(rec_a[:3]) + 1e-7).all(), (rec_b, rec_a)
-    assert (lp_a - lp_b).abs().max().item() <= 2e-5
+    assert (np.abs(rec_b[:3] - rec_a[:3]) <= 1e-4 * np.abs(rec_a[:3]) + 1e-7).all(), (rec_b, rec_a)
+    assert (lp_a - lp_b).abs().max().item() <= 5e-5
     rows = np.flatnonzero(mask == 1)[:: max(1, int(mask.sum()) // 64)][:64]
     x, lse = host_rows(hidden, lm_head, V, rows)
-    assert np.abs(lse_b.cpu().numpy()[rows] - lse).max() <= 2e-5
-    assert np.abs(lp_b.cpu().numpy()[rows] - (x[np.arange(rows.size), sel[rows]] - lse)).max() <= 2e-5
+    assert np.abs(lse_b.cpu().numpy()[rows] - lse).max() <= 5e-5
+    assert np.abs(lp_b.cpu().numpy()[rows] - (x[np.arange(rows.size), sel[rows]] - lse)).max() <= 5e-5
 
 
 def test_fused_projection_rejects_bad_arguments():
