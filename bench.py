@@ -479,16 +479,25 @@ def lmhead_config(dev, flush, passes: int = 12) -> dict:
     N = n_seq * T
     rng = np.random.Generator(np.random.PCG64(11))
     gen = torch.Generator(device=dev).manual_seed(11)
-    hidden = torch.empty(N, C, device=dev).normal_(0.0, 1.0, generator=gen)
-    lm_head = torch.empty(P, C, device=dev).normal_(0.0, 3.0 / C ** 0.5, generator=gen)
+    # inputs exactly representable in TF32 (low 13 mantissa bits cleared), so that the tensor cores' and the
+    # library matmul's own roundings of the inputs cannot differ and the two losses below are comparable
+    def tf32_representable(x):
+        return (x.view(torch.int32) & -8192).view(torch.float32)
+
+    hidden = tf32_representable(torch.empty(N, C, device=dev).normal_(0.0, 1.0, generator=gen))
+    lm_head = tf32_representable(torch.empty(P, C, device=dev).normal_(0.0, 3.0 / C ** 0.5, generator=gen))
     mask_h = W.prefix_mask(rng.integers(32, T + 1, n_seq), T)
     sel_h = np.where(mask_h == 1, rng.integers(0, V, N), -1).astype(np.int32)
     adv_h = W.group_advantages_np((rng.random(n_seq) < 0.5).astype(np.float32), n_seq // 8, 8)
     to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     mask, sel, adv = to(mask_h), to(sel_h), to(adv_h)
     weights, _ = D.weights_from_lengths(D.count_lengths(mask, n_seq, T), W.TOKEN_MEAN, 0.0)
-    old = torch.full((N,), -11.5, device=dev)
-    ref = torch.full((N,), -11.4, device=dev)
+    # old/ref log-probabilities near the true ones, as in training: log p(selected) from the fused operator + noise
+    _, now, _ = D.lmhead_loss(hidden, lm_head, V, torch.zeros(N, device=dev), torch.zeros(N, device=dev), sel, adv, weights,
+                              mask, T, CLIP_EPS, BETA, want_selected_logp=True)
+    noise = lambda: to((0.05 * rng.standard_normal(N)).astype(np.float32))
+    old = torch.where(mask == 1, now + noise(), torch.zeros_like(now))
+    ref = torch.where(mask == 1, now + noise(), torch.zeros_like(now))
     med, mean, best = time_passes(lambda: D.lmhead_loss(hidden, lm_head, V, old, ref, sel, adv, weights, mask, T, CLIP_EPS, BETA),
                                   lambda: flush(), passes)
     fused_rec = D.lmhead_loss(hidden, lm_head, V, old, ref, sel, adv, weights, mask, T, CLIP_EPS, BETA)[0].cpu().tolist()
