@@ -8,15 +8,16 @@
 //
 // Arithmetic: TF32 inputs (fp32 words whose low 13 mantissa bits the tensor core ignores), fp32
 // accumulation -- the precision of the cuBLAS TF32 matmul llm.c runs this projection with, not
-// narrower.  One CTA owns 128 rows and a contiguous range of 256-column vocabulary tiles:
+// narrower.  A tile unit is 128 rows by 256 vocabulary columns; per CTA:
 //   warp 0     TMA producer: per k-block of 32 floats, the 128 x 32 tile of hidden and the 256 x 32 tile
 //              of W into a 4-stage ring (cp.async.bulk.tensor, 128-byte swizzle, no multicast);
 //   warp 1     issues tcgen05.mma (M=128, N=256, K=8, kind::tf32), accumulators in tensor memory,
 //              two buffers of 256 columns so that a tile's epilogue overlaps the next tile's MMAs;
 //   warps 2-5  epilogue: tcgen05.ld of the accumulators (one row per thread), running maximum and
 //              sum of exponentials, the selected logit when its column passes by.
-// The vocabulary is split over several CTAs per row block so that all SMs work; a small kernel
-// merges the splits into the row records the reduce kernel of the logits path consumes.
+// The (row block, vocabulary tile) units are cut into equal contiguous shares, one per SM, so a row block's
+// vocabulary is covered by several CTAs (and a CTA may finish one row block and start the next); a small
+// kernel merges the shares into the row records the reduce kernel of the logits path consumes.
 // Every mbarrier wait is bounded; a wait that runs out raises the status word and the CTA winds down.
 #include <cuda.h>
 
@@ -46,12 +47,23 @@ constexpr long long kWaitLimit = 1LL << 31;  // about a second of SM clock
 struct LmHeadArgs {
     long long n_rows;
     int V, P, C;
-    int n_mtiles, n_splits, tiles_per_split, n_tiles;
+    int n_mtiles, n_tiles, n_ctas, max_slots;  // work = n_mtiles * n_tiles tile units, cut evenly over n_ctas CTAs
     const int32_t* selected;
     const int32_t* mask;
-    float4* partials;  // [n_splits][n_mtiles * 128]: {max, sum relative to max, selected logit, has selected}
+    float4* partials;  // [max_slots][n_mtiles * 128]: {max, sum relative to max, selected logit, has selected}
     int* status;
 };
+
+// The tile units (row block m, vocabulary tile t) are numbered m * n_tiles + t and cut into n_ctas contiguous
+// ranges of nearly equal length; a range may end one row block and start the next.  A row block's partial
+// results are numbered by the order of the CTAs that work on it ("slots").
+__host__ __device__ inline long long unit_begin(int cta, long long total, int n_ctas) { return total * cta / n_ctas; }
+__host__ __device__ inline int cta_of_unit(long long unit, long long total, int n_ctas) {
+    int c = static_cast<int>((unit * n_ctas) / total);  // a first guess that is at most one off
+    while (c + 1 < n_ctas && unit_begin(c + 1, total, n_ctas) <= unit) c++;
+    while (c > 0 && unit_begin(c, total, n_ctas) > unit) c--;
+    return c;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -150,10 +162,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const int m_tile = blockIdx.x % a.n_mtiles;
-    const int split = blockIdx.x / a.n_mtiles;
-    const int t0 = split * a.tiles_per_split;
-    const int t1 = min(t0 + a.tiles_per_split, a.n_tiles);
+    const long long total_units = static_cast<long long>(a.n_mtiles) * a.n_tiles;
+    const long long u0 = unit_begin(blockIdx.x, total_units, a.n_ctas);
+    const long long u1 = unit_begin(blockIdx.x + 1, total_units, a.n_ctas);
     const int k_blocks = a.C / kBK;
 
     if (tid == 0) {
@@ -182,7 +193,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         // ---- producer
         if (lane == 0) {
             unsigned it = 0;
-            for (int t = t0; t < t1 && abort_sh == 0; t++) {
+            for (long long u = u0; u < u1 && abort_sh == 0; u++) {
+                const int m_tile = static_cast<int>(u / a.n_tiles), t = static_cast<int>(u % a.n_tiles);
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const unsigned s = it % kStages;
                     if (!bar_wait(&empty_bar[s], ((it / kStages) & 1u) ^ 1u)) {
@@ -201,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) {
             unsigned it = 0;
             int n_done = 0;
-            for (int t = t0; t < t1 && abort_sh == 0; t++, n_done++) {
+            for (long long u = u0; u < u1 && abort_sh == 0; u++, n_done++) {
                 const unsigned ab = n_done & 1u;
                 if (!bar_wait(&acc_empty[ab], ((n_done >> 1) & 1u) ^ 1u)) {
                     atomicExch(&abort_sh, 1);
@@ -230,13 +242,25 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else {
         // ---- epilogue: thread <-> row (lane of tensor memory); a warp reaches lanes 32 * (warp % 4) ...
         const int quarter = warp & 3;
-        const long long row = static_cast<long long>(m_tile) * kBM + quarter * 32 + lane;
-        const bool row_ok = row < a.n_rows;
-        int sel = -1;
-        if (row_ok && a.mask[row] != 0) sel = a.selected[row];
+        int m_tile = -1, sel = -1;
         float m_run = kNegInfF, s_run = 0.0f, x_sel = 0.0f, has_sel = 0.0f;
+        // this CTA's partial of row block m goes to the slot numbered by the CTAs that work on that block
+        auto flush = [&](int m) {
+            const int slot = blockIdx.x - cta_of_unit(static_cast<long long>(m) * a.n_tiles, total_units, a.n_ctas);
+            const size_t at = (static_cast<size_t>(slot) * a.n_mtiles + m) * kBM + quarter * 32 + lane;
+            a.partials[at] = make_float4(m_run, s_run, x_sel, has_sel);
+        };
         int n_done = 0;
-        for (int t = t0; t < t1; t++, n_done++) {
+        for (long long u = u0; u < u1; u++, n_done++) {
+            const int m_now = static_cast<int>(u / a.n_tiles), t = static_cast<int>(u % a.n_tiles);
+            if (m_now != m_tile) {  // a new row block: hand over the finished one, start afresh
+                if (m_tile >= 0) flush(m_tile);
+                m_tile = m_now;
+                const long long row = static_cast<long long>(m_tile) * kBM + quarter * 32 + lane;
+                sel = (row < a.n_rows && a.mask[row] != 0) ? a.selected[row] : -1;
+                m_run = kNegInfF;
+                s_run = x_sel = has_sel = 0.0f;
+            }
             const unsigned ab = n_done & 1u;
             bool ok = abort_sh == 0;
             if (ok) ok = bar_wait(&acc_full[ab], (n_done >> 1) & 1u);
@@ -278,10 +302,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             __syncwarp();
             if (lane == 0) bar_arrive(&acc_empty[ab]);  // the buffer may be overwritten by the tile after next
         }
-        if (row_ok || true) {
-            const size_t at = static_cast<size_t>(split) * a.n_mtiles * kBM + static_cast<size_t>(m_tile) * kBM + quarter * 32 + lane;
-            a.partials[at] = make_float4(m_run, s_run, x_sel, has_sel);
-        }
+        if (m_tile >= 0) flush(m_tile);
     }
 
     // ---- wind down: nothing of this CTA is still in flight, then the tensor memory goes back
@@ -298,12 +319,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 // Merges the vocabulary splits of every row into the record the reduce kernel consumes: the row maximum,
 // the normaliser relative to it (in double) and the selected logit; a missing selected logit (an id outside
 // the vocabulary) is flagged as a bad input.  Also clears the pass's control words for the reduce kernel.
-__global__ void __launch_bounds__(256) lmhead_merge_kernel(const float4* __restrict__ partials, int n_splits,
-                                                           long long padded_rows, LogitsArgs a, double* lse_out) {
+__global__ void __launch_bounds__(256) lmhead_merge_kernel(const float4* __restrict__ partials, int n_mtiles, int n_tiles,
+                                                           int n_ctas, LogitsArgs a, double* lse_out) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *a.counter = 0u;  // (the status word was cleared before the first kernel)
     const long long row = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
     if (row >= a.n_rows) return;
     const bool active = a.mask[row] != 0;
+    // the CTAs that worked on this row's block, first to last: as many slots hold a partial
+    const long long total_units = static_cast<long long>(n_mtiles) * n_tiles, padded_rows = static_cast<long long>(n_mtiles) * kBM;
+    const int m_tile = static_cast<int>(row / kBM);
+    const int n_splits = cta_of_unit(static_cast<long long>(m_tile + 1) * n_tiles - 1, total_units, n_ctas) -
+                         cta_of_unit(static_cast<long long>(m_tile) * n_tiles, total_units, n_ctas) + 1;
     float m = kNegInfF;
     for (int s = 0; s < n_splits; s++) m = fmaxf(m, partials[static_cast<size_t>(s) * padded_rows + row].x);
     double z = 0.0;
@@ -360,7 +386,7 @@ cudaError_t make_map(EncodeTiled encode, CUtensorMap* map, const float* base, lo
 }
 
 struct LmHeadPlan {
-    int n_mtiles, n_tiles, n_splits, tiles_per_split;
+    int n_mtiles, n_tiles, n_ctas, max_slots;
     long long padded_rows;
 };
 
@@ -368,11 +394,11 @@ LmHeadPlan plan_for(long long n_rows, int P, int sms) {
     LmHeadPlan p;
     p.n_mtiles = static_cast<int>((n_rows + kBM - 1) / kBM);
     p.n_tiles = (P + kBN - 1) / kBN;
-    int splits = sms / p.n_mtiles;  // one CTA per SM: as many vocabulary splits as keep every SM busy once
-    if (splits < 1) splits = 1;
-    if (splits > p.n_tiles) splits = p.n_tiles;
-    p.tiles_per_split = (p.n_tiles + splits - 1) / splits;
-    p.n_splits = (p.n_tiles + p.tiles_per_split - 1) / p.tiles_per_split;
+    const long long total = static_cast<long long>(p.n_mtiles) * p.n_tiles;
+    p.n_ctas = static_cast<int>(total < sms ? total : sms);  // one CTA per SM, every SM busy, equal shares of the tiles
+    // a row block's tiles are shared by at most this many consecutive CTAs
+    const long long shortest = total / p.n_ctas;
+    p.max_slots = static_cast<int>((p.n_tiles + shortest - 1) / shortest) + 1;
     p.padded_rows = static_cast<long long>(p.n_mtiles) * kBM;
     return p;
 }
@@ -396,7 +422,7 @@ size_t grpo_b200_lmhead_workspace_bytes(int64_t n_rows, int P) {
     const LmHeadPlan p = plan_for(n_rows, P, device_sms());
     // the logits path's workspace (row records, control words, reduce partials), then the split partials
     const size_t base = (grpo_b200_logits_workspace_bytes(n_rows) + 255) & ~static_cast<size_t>(255);
-    return base + static_cast<size_t>(p.n_splits) * static_cast<size_t>(p.padded_rows) * sizeof(float4);
+    return base + static_cast<size_t>(p.max_slots) * static_cast<size_t>(p.padded_rows) * sizeof(float4);
 }
 
 int grpo_b200_lmhead_loss(const float* hidden, const float* lm_head, int64_t n_rows, int C, int V, int P,
@@ -460,9 +486,9 @@ int grpo_b200_lmhead_loss(const float* hidden, const float* lm_head, int64_t n_r
     h.P = P;
     h.C = C;
     h.n_mtiles = plan.n_mtiles;
-    h.n_splits = plan.n_splits;
-    h.tiles_per_split = plan.tiles_per_split;
     h.n_tiles = plan.n_tiles;
+    h.n_ctas = plan.n_ctas;
+    h.max_slots = plan.max_slots;
     h.selected = selected;
     h.mask = mask;
     h.partials = reinterpret_cast<float4*>(static_cast<unsigned char*>(workspace) + base);
@@ -482,10 +508,10 @@ int grpo_b200_lmhead_loss(const float* hidden, const float* lm_head, int64_t n_r
         }
     }
     GRPO_CUDA_TRY(cudaMemsetAsync(a.status, 0, 32, s));
-    lmhead_stats_kernel<<<static_cast<unsigned>(plan.n_mtiles * plan.n_splits), kThreads, kSmemBytes, s>>>(map_a, map_b, h);
+    lmhead_stats_kernel<<<static_cast<unsigned>(plan.n_ctas), kThreads, kSmemBytes, s>>>(map_a, map_b, h);
     GRPO_CUDA_TRY(cudaGetLastError());
-    lmhead_merge_kernel<<<static_cast<unsigned>((n_rows + 255) / 256), 256, 0, s>>>(h.partials, plan.n_splits, plan.padded_rows, a,
-                                                                                   lse_out);
+    lmhead_merge_kernel<<<static_cast<unsigned>((n_rows + 255) / 256), 256, 0, s>>>(h.partials, plan.n_mtiles, plan.n_tiles,
+                                                                                   plan.n_ctas, a, lse_out);
     GRPO_CUDA_TRY(cudaGetLastError());
     ExchangeArgs x = {};
     GRPO_CUDA_TRY(launch_logits_reduce(a, x, s));
