@@ -187,10 +187,25 @@ int validate_inputs(const float* lp_new, size_t n_new, const float* lp_old, size
     if (int rc = expect_size("logp_ref", n_ref, shape.tokens)) return rc;
     if (int rc = expect_size("advantages", n_adv, shape.sequences)) return rc;
     if (int rc = expect_size("mask", n_mask, shape.tokens)) return rc;
+    // one branch-free sweep first (it vectorises); only a batch that has a bad value is walked again in the
+    // reference's order to find which complaint comes first
+    unsigned bad = 0;
+    const uint32_t* old_bits = reinterpret_cast<const uint32_t*>(lp_old);
+    const uint32_t* ref_bits = reinterpret_cast<const uint32_t*>(lp_ref);
     for (size_t i = 0; i < shape.tokens; i++) {
-        if ((lp_new && !std::isfinite(lp_new[i])) || !std::isfinite(lp_old[i]) || !std::isfinite(lp_ref[i]))
-            return invalid("log probabilities must be finite");
-        if (mask[i] != 0 && mask[i] != 1) return invalid("mask values must be 0 or 1");
+        bad |= ((old_bits[i] & 0x7f800000u) == 0x7f800000u) | ((ref_bits[i] & 0x7f800000u) == 0x7f800000u) |
+               (static_cast<uint32_t>(mask[i]) > 1u);
+    }
+    if (lp_new) {
+        const uint32_t* new_bits = reinterpret_cast<const uint32_t*>(lp_new);
+        for (size_t i = 0; i < shape.tokens; i++) bad |= (new_bits[i] & 0x7f800000u) == 0x7f800000u;
+    }
+    if (bad) {
+        for (size_t i = 0; i < shape.tokens; i++) {
+            if ((lp_new && !std::isfinite(lp_new[i])) || !std::isfinite(lp_old[i]) || !std::isfinite(lp_ref[i]))
+                return invalid("log probabilities must be finite");
+            if (mask[i] != 0 && mask[i] != 1) return invalid("mask values must be 0 or 1");
+        }
     }
     for (size_t s = 0; s < shape.sequences; s++)
         if (!std::isfinite(adv[s])) return invalid("advantages must be finite");
@@ -228,6 +243,9 @@ int make_weights(const int32_t* mask, const Shape& shape, int T, const Options& 
 namespace host {
 int check_selected(const int32_t* selected, const int32_t* mask, size_t n, int V, size_t& first_bad) {
     first_bad = n;
+    unsigned any = 0;  // branch-free sweep first; the index is only looked for when there is one
+    for (size_t i = 0; i < n; i++) any |= (mask[i] != 0) & (static_cast<uint32_t>(selected[i]) >= static_cast<uint32_t>(V));
+    if (!any) return 0;
     for (size_t i = 0; i < n; i++)
         if (mask[i] != 0 && (selected[i] < 0 || selected[i] >= V)) {
             first_bad = i;
@@ -271,7 +289,8 @@ struct LogitsMeta {
 };
 
 size_t logits_meta_bytes(const Shape& shape) {
-    return 4 * slice(shape.tokens * 4) + 2 * slice(shape.sequences * 4) + slice((shape.tokens + 2) * 4) +
+    return 4 * slice(shape.tokens * 4) + 2 * slice(shape.sequences * 4) +
+           slice(grpo_b200_row_order_bytes(static_cast<int64_t>(shape.tokens))) +
            slice(sizeof(grpo_b200_result_t)) +
            slice(grpo_b200_logits_workspace_bytes(static_cast<int64_t>(shape.tokens)));
 }
@@ -281,7 +300,7 @@ size_t logits_meta_bytes(const Shape& shape) {
 // device layout and issues the single upload.
 cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, const float* lp_old,
                               const float* lp_ref, const int32_t* selected, const float* adv,
-                              const float* weights, const int32_t* mask, LogitsMeta& m) {
+                              const float* weights, const int32_t* mask, LogitsMeta& m, bool order_on_device = false) {
     const size_t n = shape.tokens, s = shape.sequences;
     char* dev_start = bump.base + bump.off;
     m.old_d = bump.take<float>(n);
@@ -290,8 +309,9 @@ cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, cons
     m.mask_d = bump.take<int32_t>(n);
     m.adv_d = bump.take<float>(s);
     m.w_d = bump.take<float>(s);
-    m.order_d = bump.take<int32_t>(n + 2);
-    const size_t packed = static_cast<size_t>(bump.base + bump.off - dev_start);
+    size_t packed = static_cast<size_t>(bump.base + bump.off - dev_start);  // what travels in the one upload
+    m.order_d = bump.take<int32_t>(grpo_b200_row_order_bytes(static_cast<int64_t>(n)) / sizeof(int32_t));
+    if (!order_on_device) packed = static_cast<size_t>(reinterpret_cast<char*>(m.order_d + n + 2) - dev_start);
     m.result_d = bump.take<grpo_b200_result_t>(1);
     m.work_bytes = grpo_b200_logits_workspace_bytes(static_cast<int64_t>(n));
     m.work_d = bump.take<char>(m.work_bytes);
@@ -306,7 +326,7 @@ cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, cons
     put(mask, n * 4, m.mask_d);
     put(adv, s * 4, m.adv_d);
     put(weights, s * 4, m.w_d);
-    {
+    if (!order_on_device) {
         int32_t* order_h = reinterpret_cast<int32_t*>(h + (reinterpret_cast<char*>(m.order_d) - dev_start));
         size_t n_active = 0;
         for (size_t i = 0; i < n; i++) n_active += mask[i] != 0;
@@ -317,7 +337,11 @@ cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, cons
         for (size_t i = 0; i < n; i++) *(mask[i] != 0 ? active : masked)++ = static_cast<int32_t>(i);
     }
     m.result_h = reinterpret_cast<grpo_b200_result_t*>(arena.pinned + slice(packed));
-    return cudaMemcpyAsync(dev_start, h, packed, cudaMemcpyHostToDevice, nullptr);
+    cudaError_t err = cudaMemcpyAsync(dev_start, h, packed, cudaMemcpyHostToDevice, nullptr);
+    // the partition of the rows by mask: two small launches behind the upload instead of two host passes and 4 bytes
+    // per row more to upload
+    if (err == cudaSuccess && order_on_device) err = launch_row_order(m.mask_d, static_cast<long long>(n), m.order_d, nullptr);
+    return err;
 }
 
 }  // namespace
@@ -418,7 +442,7 @@ int grpo_b200_logits_device_inplace_host(float* logits_and_dlogits, const float*
     Bump bump(arena.dev);
     LogitsMeta m;
     GRPO_CUDA_TRY(stage_logits_meta(arena, bump, shape, logp_old, logp_ref, selected, advantages, weights.data(),
-                                    mask, m));
+                                    mask, m, /*order_on_device=*/true));
     if (int rc = grpo_b200_logits(logits_and_dlogits, logits_and_dlogits, m.old_d, m.ref_d, m.sel_d, m.adv_d,
                                   m.w_d, m.mask_d, static_cast<int64_t>(shape.tokens), 0, T, V, P, clip_eps, beta,
                                   kernel, 0, nullptr, m.order_d, m.result_d, m.work_d, m.work_bytes, nullptr))
