@@ -143,10 +143,19 @@ __device__ __forceinline__ RowScalars load_row_scalars(const LogitsArgs& a, long
 // reduce kernel, which redoes the same step in double, off this kernel's critical path, for the
 // three loss sums (a cancelling sum that needs the reference's double log-sum-exp).
 // z is the normaliser relative to e^row_max.  Follows src/cpu/grpo_loss.cpp:214-215, :137-160.
-__device__ __forceinline__ RowBroadcast row_leader_fast(const LogitsArgs& a, long long row, float row_max, double z,
+// z arrives as a double or as an fp32 head + tail.
+struct FF {
+    float hi, lo;
+};
+__device__ __forceinline__ float z_as_float(double z) { return static_cast<float>(z); }
+__device__ __forceinline__ float z_as_float(FF z) { return __fadd_rn(z.hi, z.lo); }
+__device__ __forceinline__ double z_as_double(double z) { return z; }
+__device__ __forceinline__ double z_as_double(FF z) { return static_cast<double>(z.hi) + static_cast<double>(z.lo); }
+template <class Z>
+__device__ __forceinline__ RowBroadcast row_leader_fast(const LogitsArgs& a, long long row, float row_max, Z z,
                                                         float x_sel, int sel, const RowScalars& sc, bool bad_input,
                                                         bool write_record) {
-    const float zf = static_cast<float>(z);
+    const float zf = z_as_float(z);
     const float lp_new = x_sel - (row_max + logf(zf));
     const TokenTerms t = token_terms<false>(lp_new, sc.lp_old, sc.lp_ref, sc.adv, sc.w, a.clip_eps, a.beta);
     RowBroadcast b;
@@ -155,7 +164,7 @@ __device__ __forceinline__ RowBroadcast row_leader_fast(const LogitsArgs& a, lon
     b.selected = sel;
     if (write_record) {
         RowRecord r;
-        r.z = z;
+        r.z = z_as_double(z);
         r.m = row_max;
         r.x_sel = x_sel;
         r.flags = bad_input ? kRowBadInput : 0.0f;
@@ -209,40 +218,96 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  : "memory");
 }
 
-// 2^t in double for t in about [-60, 1], to ~3e-10 relative: 2^k * 2^r with r = t - k in [-1/2, 1/2]
-// and a degree-8 polynomial in r (Taylor coefficients of exp(r ln 2)).  About a dozen dependent
-// double operations instead of the library routine's several dozen: this sits on every thread's
-// path once or twice per row.
-__device__ __forceinline__ double exp2_small_d(double t) {
-    const double kf = rint(t);
-    const double r = t - kf;
-    double p = 1.3215486790144309e-06;   // ln2^8 / 8!
-    p = fma(p, r, 1.5252733804059841e-05);  // ln2^7 / 7!
-    p = fma(p, r, 1.5403530393381609e-04);  // ln2^6 / 6!
-    p = fma(p, r, 1.3333558146428443e-03);  // ln2^5 / 5!
-    p = fma(p, r, 9.6181291076284772e-03);  // ln2^4 / 4!
-    p = fma(p, r, 5.5504108664821580e-02);  // ln2^3 / 3!
-    p = fma(p, r, 2.4022650695910071e-01);  // ln2^2 / 2!
-    p = fma(p, r, 6.9314718055994531e-01);  // ln2
-    p = fma(p, r, 1.0);
-    return p * __hiloint2double((1023 + static_cast<int>(kf)) << 20, 0);
+// ---- float-float arithmetic: a value carried as an fp32 head plus an fp32 tail (about 48 bits).
+// The per-row path of the pipelined kernel needs terms and factors good to ~1e-8 relative; double
+// precision gives that, but its dependent chains sat on every thread's path twice per row and cost
+// a sixth of the kernel's bandwidth.  These few fp32 instructions give the same digits.
+// a + b exactly: head = fl(a + b), tail = the rounding error (symmetric in a and b, bit for bit)
+__device__ __forceinline__ FF two_sum(float a, float b) {
+    const float s = __fadd_rn(a, b);
+    const float bb = __fsub_rn(s, a);
+    return FF{s, __fadd_rn(__fsub_rn(a, __fsub_rn(s, bb)), __fsub_rn(b, bb))};
+}
+// a * b exactly
+__device__ __forceinline__ FF two_prod(float a, float b) {
+    const float p = __fmul_rn(a, b);
+    return FF{p, __fmaf_rn(a, b, -p)};
+}
+// all-lanes float-float sum with a fixed butterfly; every step is symmetric in its two operands, so
+// every lane ends with the same bits
+__device__ __forceinline__ FF warp_sum_ff(FF v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float oh = __shfl_xor_sync(0xffffffffu, v.hi, o);
+        const float ol = __shfl_xor_sync(0xffffffffu, v.lo, o);
+        const FF s = two_sum(v.hi, oh);
+        v.hi = s.hi;
+        v.lo = __fadd_rn(__fadd_rn(v.lo, ol), s.lo);
+    }
+    return v;
 }
 
-// Double-precision correction of one term given its logit: what 2^(x*log2e - shift) is exactly,
-// minus the fp32 term as it entered the sum (the same deterministic function as in the main
-// sweep, so the same bits).  The exact value is divided by the ex2 bias factor because the whole
-// fp32 sum is multiplied by that factor later.
-__device__ __forceinline__ double term_correction(float xv, float shift) {
-    if (xv == kNegInf) return 0.0;
-    const double exact = exp2_small_d(fma(static_cast<double>(xv), kLog2eD, -static_cast<double>(shift)));
-    return exact * (1.0 / kEx2BiasFix) - static_cast<double>(exp_rel(xv, shift));
+// ln 2 and (ln 2)^2 / 2 as fp32 head + tail
+#define kLn2Hi 0.693147182464599609375f
+#define kLn2Lo (-1.90465432314823602e-9f)
+#define kHalfLn2SqHi 0.2402265071868896484375f
+#define kHalfLn2SqLo (-2.27788954365593099e-10f)
+// 2^(th + tl) as head + tail, |tl| tiny against |th|, th clamped to [lowest, 2] by the caller with
+// lowest >= -126.  2^k * 2^r with r = t - k in [-1/2, 1/2]; 2^r = 1 + r ln2 + r^2 ln2^2/2 carried
+// in float-float and the Taylor terms of degree 3 to 8 in plain fp32 (they sum to < 7e-3).
+// Measured against the double-precision library over 1M arguments: 5.6e-9 relative at worst.
+__device__ __forceinline__ FF exp2_ff(float th, float tl) {
+    const float k = rintf(th);
+    const FF r = two_sum(__fsub_rn(th, k), tl);
+    const float rh = r.hi;
+    float q = 1.3215486790144309e-06f;              // ln2^8 / 8!
+    q = __fmaf_rn(q, rh, 1.5252733804059841e-05f);  // ln2^7 / 7!
+    q = __fmaf_rn(q, rh, 1.5403530393381609e-04f);  // ln2^6 / 6!
+    q = __fmaf_rn(q, rh, 1.3333558146428443e-03f);  // ln2^5 / 5!
+    q = __fmaf_rn(q, rh, 9.6181291076284772e-03f);  // ln2^4 / 4!
+    q = __fmaf_rn(q, rh, 5.5504108664821580e-02f);  // ln2^3 / 3!
+    FF u = two_prod(rh, kLn2Hi);
+    u.lo = __fmaf_rn(rh, kLn2Lo, u.lo);
+    const FF v = two_prod(rh, rh);
+    FF w = two_prod(v.hi, kHalfLn2SqHi);
+    w.lo = __fmaf_rn(v.lo, kHalfLn2SqHi, __fmaf_rn(v.hi, kHalfLn2SqLo, w.lo));
+    const float tail = __fmul_rn(__fmul_rn(v.hi, rh), q);
+    const FF s1 = two_sum(1.0f, u.hi);
+    const FF s2 = two_sum(s1.hi, w.hi);
+    float lo = __fadd_rn(__fadd_rn(s1.lo, s2.lo), __fadd_rn(u.lo, w.lo));
+    lo = __fadd_rn(lo, __fmaf_rn(r.lo, kLn2Hi, tail));
+    const FF res = two_sum(s2.hi, lo);
+    const float scale = __int_as_float((static_cast<int>(k) + 127) << 23);  // 2^k exactly
+    return FF{__fmul_rn(res.hi, scale), __fmul_rn(res.lo, scale)};
+}
+
+// x * log2(e) - shift as head + tail: the product exactly, then an exact subtraction of the head
+__device__ __forceinline__ FF scaled_minus_shift(float x, float shift) {
+    const FF p = two_prod(x, kLog2eHi);
+    const FF t = two_sum(p.hi, -shift);
+    return FF{t.hi, __fadd_rn(t.lo, __fmaf_rn(x, kLog2eLo, p.lo))};
+}
+
+// Correction of one term given its logit: what 2^(x*log2e - shift) is to ~5e-9, minus the fp32
+// term as it entered the sum (the same deterministic function as in the main sweep, so the same
+// bits).  The accurate value is divided by the ex2 bias factor because the whole fp32 sum is
+// multiplied by that factor later.  The two values agree to ~2e-7, so their heads subtract exactly.
+// Terms below 2^-100 of the warp's largest have nothing to correct and are clamped there, which
+// keeps the power of two constructible.
+__device__ __forceinline__ float term_correction(float xv, float shift) {
+    if (xv == kNegInf) return 0.0f;
+    const FF t = scaled_minus_shift(xv, shift);
+    const FF e = exp2_ff(fmaxf(t.hi, -100.0f), t.lo);
+    constexpr float kInvBiasMinus1 = static_cast<float>(1.0 / kEx2BiasFix - 1.0);
+    return __fadd_rn(__fsub_rn(e.hi, exp_rel(xv, shift)), __fmaf_rn(e.hi, kInvBiasMinus1, e.lo));
 }
 
 // One warp's partial of the row reduction.  Lane 0 of every consumer warp writes it into the same
 // slot of EVERY CTA of the cluster (its own included) and then arrives on that CTA's exchange
 // barrier, so the first thing any CTA waits for after its exponentials is the complete set.
 struct __align__(16) WarpPart {
-    double s;     // sum of the warp's terms 2^(x*log2e - shift), compensated, double corrections included
+    float s_hi;   // sum of the warp's terms 2^(x*log2e - shift) as head + tail: compensated fp32 sums
+    float s_lo;   // with the corrections of the dominant terms folded into the tail
     float m;      // maximum of the warp's columns (-inf when it holds none)
     float shift;  // the exponent offset the warp used
     float chk;    // finiteness probe
@@ -253,14 +318,13 @@ struct __align__(16) WarpPart {
 
 // Asynchronous 32-byte store of one partial into CTA `rank`'s copy of `slot`; each 16-byte half
 // counts its bytes on that CTA's copy of `bar` when it lands (st.async, sm_90+).
-__device__ __forceinline__ void send_part(WarpPart* slot, uint64_t* bar, unsigned rank, double s, float m, float shift,
+__device__ __forceinline__ void send_part(WarpPart* slot, uint64_t* bar, unsigned rank, FF s, float m, float shift,
                                           float chk, float x_sel, int has_sel) {
     uint32_t dst, rbar;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(smem_addr(slot)), "r"(rank));
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(smem_addr(bar)), "r"(rank));
-    const long long s_bits = __double_as_longlong(s);
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst),
-                 "r"(static_cast<int>(s_bits & 0xffffffffLL)), "r"(static_cast<int>(s_bits >> 32)), "r"(__float_as_int(m)),
+                 "r"(__float_as_int(s.hi)), "r"(__float_as_int(s.lo)), "r"(__float_as_int(m)),
                  "r"(__float_as_int(shift)), "r"(rbar)
                  : "memory");
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst + 16u),
@@ -305,9 +369,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 // Issuing a bulk copy can itself stall for a long time when the copy queue is full, which is
 // why a dedicated warp does it.
 // ---------------------------------------------------------------------------------------------
-template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, bool CHECK>
-__global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (THREADS * VEC >= 4096 ? 2 : 4))
-    logits_pipelined_kernel(const LogitsArgs a) {
+template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, int MINB, bool CHECK>
+__global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(const LogitsArgs a) {
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE_CHUNKS = TJ * THREADS;
     constexpr int TILES = VEC / TJ;
@@ -321,7 +384,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
     __shared__ uint64_t empty_bar[STAGES];
     __shared__ uint64_t xbar[2];                    // [row parity]: completes when all CLUSTER * WARPS partials are in
     __shared__ WarpPart parts[2][CLUSTER * WARPS];  // [row parity][source rank * WARPS + source warp]
-    __shared__ double warp_f[WARPS];  // 2^(shift_w - M*log2e): the warp's terms relative to the row maximum
+    __shared__ float warp_f[WARPS];  // 2^(shift_w - M*log2e): the warp's terms relative to the row maximum
     __shared__ RowBroadcast bc;
     __shared__ int meta_sel[BATCH];
     __shared__ float meta_old[BATCH];
@@ -630,15 +693,17 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                     kahan_add2(sb, ncb, eb);
                 }
             }
-            const double s_thread = ((static_cast<double>(sa.x) + static_cast<double>(nca.x)) +
-                                     (static_cast<double>(sa.y) + static_cast<double>(nca.y))) +
-                                    ((static_cast<double>(sb.x) + static_cast<double>(ncb.x)) +
-                                     (static_cast<double>(sb.y) + static_cast<double>(ncb.y)));
-            // Every thread redoes its two largest chunk maxima in double: a row's few dominant terms
+            // the thread's total as head + tail: the four sums add exactly (two_sum), their
+            // compensations and rounding errors collect in the tail
+            const FF t01 = two_sum(sa.x, sa.y), t23 = two_sum(sb.x, sb.y);
+            const FF t4 = two_sum(t01.hi, t23.hi);
+            float s_tail = __fadd_rn(__fadd_rn(__fadd_rn(nca.x, nca.y), __fadd_rn(ncb.x, ncb.y)),
+                                     __fadd_rn(__fadd_rn(t01.lo, t23.lo), t4.lo));
+            // Every thread redoes its two largest chunk maxima to ~5e-9: a row's few dominant terms
             // are among them, and those are the terms whose fp32 error (~1e-7 each) the
             // log-sum-exp cannot absorb.  Everything else is light enough to average out.
-            const double s_fixed = s_thread + (term_correction(m, shift) + term_correction(m2, shift));
-            const double s_warp = warp_sum_all(s_fixed);
+            s_tail = __fadd_rn(s_tail, __fadd_rn(term_correction(m, shift), term_correction(m2, shift)));
+            const FF s_warp = warp_sum_ff(FF{t4.hi, s_tail});
             if (CHECK) chk = warp_sum_f(chk);
 
             // ---- every warp hands its partial to every CTA of the cluster: lane p sends it to CTA p
@@ -647,7 +712,8 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             if (CLUSTER == 1) {
                 if (lane == 0) {
                     WarpPart mine;
-                    mine.s = s_warp;
+                    mine.s_hi = s_warp.hi;
+                    mine.s_lo = s_warp.lo;
                     mine.m = m_warp;
                     mine.shift = shift;
                     mine.chk = chk;
@@ -683,25 +749,37 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
                     if (idx < PARTS) m_lane = fmaxf(m_lane, in[idx].m);
                 }
                 const float m_row = warp_max(m_lane);
-                const double row_shift = static_cast<double>(m_row) * kLog2eD;
-                double s = 0.0;
+                // m_row * log2(e) as head + tail
+                const FF row_shift_p = two_prod(m_row, kLog2eHi);
+                const float row_shift_lo = __fmaf_rn(m_row, kLog2eLo, row_shift_p.lo);
+                FF s = FF{0.0f, 0.0f};
                 float c = 0.0f, xs = 0.0f;
 #pragma unroll
                 for (int i = 0; i < PER_LANE; i++) {
                     const int idx = lane + 32 * i;
                     if (idx < PARTS) {
                         const WarpPart part = in[idx];
-                        // the warp's terms are 2^(x*log2e - shift); relative to e^m_row they scale by f
-                        double f = 0.0;
-                        if (part.m != kNegInf)
-                            f = exp2_small_d(fmax(static_cast<double>(part.shift) - row_shift, -1000.0)) * kEx2BiasFix;
-                        s += part.s * f;
+                        // the warp's terms are 2^(x*log2e - shift); relative to e^m_row they scale by
+                        // f = 2^(shift - m_row*log2e) * (ex2 bias factor).  Warps more than 2^-120
+                        // below the row maximum are clamped there: they cannot reach the sum.
+                        FF f = FF{0.0f, 0.0f};
+                        if (part.m != kNegInf) {
+                            const FF d = two_sum(part.shift, -row_shift_p.hi);
+                            f = exp2_ff(fmaxf(d.hi, -120.0f), __fsub_rn(d.lo, row_shift_lo));
+                            f.lo = __fmaf_rn(f.hi, static_cast<float>(kEx2BiasFix - 1.0), f.lo);
+                        }
+                        // s += part.s * f in float-float
+                        const FF ph = two_prod(part.s_hi, f.hi);
+                        const float pl = __fmaf_rn(part.s_hi, f.lo, __fmaf_rn(part.s_lo, f.hi, ph.lo));
+                        const FF acc = two_sum(s.hi, ph.hi);
+                        s.hi = acc.hi;
+                        s.lo = __fadd_rn(__fadd_rn(s.lo, pl), acc.lo);
                         if (CHECK) c += part.chk;
                         if (part.has_sel) xs += part.x_sel;  // exactly one warp of the cluster holds it
-                        if (idx / WARPS == static_cast<int>(crank)) warp_f[idx % WARPS] = f;
+                        if (idx / WARPS == static_cast<int>(crank)) warp_f[idx % WARPS] = __fadd_rn(f.hi, f.lo);
                     }
                 }
-                const double z_row = warp_sum_all(s);
+                const FF z_row = warp_sum_ff(s);
                 if (CHECK) c = warp_sum_f(c);
                 x_sel = warp_sum_f(xs);
                 // ---- row leader: dlogp for the backward sweep and the row's record.  Every CTA of
@@ -714,7 +792,7 @@ __global__ void __launch_bounds__(THREADS + 32, (THREADS * VEC >= 8192) ? 1 : (T
             consumer_sync(THREADS);
             // ---- backward sweep from registers: g * (onehot - p) = e_i * coef + [i == sel] * g
             const RowBroadcast b = bc;
-            const float coef = static_cast<float>(warp_f[warp]) * b.neg_g_over_z;
+            const float coef = warp_f[warp] * b.neg_g_over_z;
             if (special_j >= 0) {  // padding columns inside the chunk that straddles V come back as +0
 #pragma unroll
                 for (int j = 0; j < VEC; j++) {
@@ -1076,12 +1154,25 @@ constexpr Variant kVariants[] = {
     {8, 128, 16, 4, 6, "8x128x16"},   // 3: <=  65536   (GPT-2's 50,304)
     {8, 256, 16, 4, 6, "8x256x16"},   // 4: <= 131072   96 KB ring, two CTAs per SM
     {8, 512, 16, 4, 6, "8x512x16"},   // 5: <= 262144   192 KB ring of 32 KB stages, one CTA per SM
+#ifdef GRPO_EXPERIMENT_VARIANTS
+    {8, 128, 16, 4, 6, "8x128x16b3"},
+    {8, 128, 14, 2, 12, "8x128x14"},
+    {8, 256, 8, 2, 6, "8x256x8b3"},
+    {8, 256, 8, 2, 6, "8x256x8b2"},
+    {8, 192, 9, 3, 5, "8x192x9b4"},
+    {8, 192, 9, 3, 5, "8x192x9b3"},
+    {8, 256, 7, 1, 12, "8x256x7b3"},
+    {8, 128, 8, 4, 4, "8x128x8b6"},
+    {8, 128, 8, 4, 4, "8x128x8b5"},
+    {8, 128, 8, 2, 8, "8x128x8t2b6"},
+    {8, 128, 8, 4, 3, "8x128x8s3b7"},
+#endif
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
-template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, bool CHECK>
+template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, int MINB, bool CHECK>
 cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
-    auto kernel = logits_pipelined_kernel<THREADS, VEC, TJ, STAGES, CLUSTER, CHECK>;
+    auto kernel = logits_pipelined_kernel<THREADS, VEC, TJ, STAGES, CLUSTER, MINB, CHECK>;
     constexpr size_t ring_bytes = static_cast<size_t>(STAGES) * TJ * THREADS * sizeof(float4);
     // per device: opt in to the large dynamic shared memory and find how many clusters fit at once
     // (two host threads may fill the same entry at once: both compute the same number)
@@ -1132,12 +1223,25 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
 template <bool CHECK>
 cudaError_t launch_by_index(int variant, const LogitsArgs& a, cudaStream_t stream) {
     switch (variant) {
-        case 0: return launch_variant<128, 16, 4, 6, 1, CHECK>(a, stream);
-        case 1: return launch_variant<128, 16, 4, 6, 2, CHECK>(a, stream);
-        case 2: return launch_variant<128, 16, 4, 6, 4, CHECK>(a, stream);
-        case 3: return launch_variant<128, 16, 4, 6, 8, CHECK>(a, stream);
-        case 4: return launch_variant<256, 16, 4, 6, 8, CHECK>(a, stream);
-        case 5: return launch_variant<512, 16, 4, 6, 8, CHECK>(a, stream);
+        case 0: return launch_variant<128, 16, 4, 6, 1, 4, CHECK>(a, stream);
+        case 1: return launch_variant<128, 16, 4, 6, 2, 4, CHECK>(a, stream);
+        case 2: return launch_variant<128, 16, 4, 6, 4, 4, CHECK>(a, stream);
+        case 3: return launch_variant<128, 16, 4, 6, 8, 4, CHECK>(a, stream);
+        case 4: return launch_variant<256, 16, 4, 6, 8, 2, CHECK>(a, stream);
+        case 5: return launch_variant<512, 16, 4, 6, 8, 1, CHECK>(a, stream);
+#ifdef GRPO_EXPERIMENT_VARIANTS
+        case 6: return launch_variant<128, 16, 4, 6, 8, 3, CHECK>(a, stream);
+        case 7: return launch_variant<128, 14, 2, 12, 8, 4, CHECK>(a, stream);
+        case 8: return launch_variant<256, 8, 2, 6, 8, 3, CHECK>(a, stream);
+        case 9: return launch_variant<256, 8, 2, 6, 8, 2, CHECK>(a, stream);
+        case 10: return launch_variant<192, 9, 3, 5, 8, 4, CHECK>(a, stream);
+        case 11: return launch_variant<192, 9, 3, 5, 8, 3, CHECK>(a, stream);
+        case 12: return launch_variant<256, 7, 1, 12, 8, 3, CHECK>(a, stream);
+        case 13: return launch_variant<128, 8, 4, 4, 8, 6, CHECK>(a, stream);
+        case 14: return launch_variant<128, 8, 4, 4, 8, 5, CHECK>(a, stream);
+        case 15: return launch_variant<128, 8, 2, 8, 8, 6, CHECK>(a, stream);
+        case 16: return launch_variant<128, 8, 4, 3, 8, 7, CHECK>(a, stream);
+#endif
         default: return cudaErrorInvalidValue;
     }
 }

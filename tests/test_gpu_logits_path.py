@@ -157,6 +157,41 @@ def test_every_resident_variant_matches_oracle():
         D.set_variant(-1)
 
 
+def test_wide_dynamic_range_rows():
+    """Rows whose logits span far more than a float exponent range in e-folds: a few columns near
+    the top and everything else one or two thousand below, inside one thread's chunks, inside one
+    warp and across warps.  The terms far below vanish against the top ones (the reference's double
+    exp gives exactly 0 for them too, src/cpu/grpo_loss.cpp:203-213), and nothing on the way may
+    overflow, lose its sign or turn into a NaN."""
+    import torch
+    V = 50257
+    b = W.logits_case(1, 2, 4, V, sigma=2.0, min_len=4, seed=77)
+    rng = np.random.Generator(np.random.PCG64(5))
+    lg = b.logits.reshape(b.N, V)
+    lg[0] = -2000.0 + rng.standard_normal(V).astype(np.float32)
+    lg[0, [5, 4097, 50000]] = [3.0, 2.5, 1.0]
+    lg[1] = np.where(np.arange(V) % 2 == 0, 300.0, -900.0).astype(np.float32) + rng.standard_normal(V).astype(np.float32)
+    lg[2] = -1500.0
+    lg[2, 12345] = 40.0
+    lg[3, : V // 2] -= 1200.0
+    lg[4] = rng.uniform(-1000.0, 1000.0, V).astype(np.float32)
+    b.selected[:5] = [5, 2, 12345, V - 1, 7]
+    # behaviour-policy and reference log-probs near the new ones, as a rollout has them
+    l64 = lg.astype(np.float64)
+    top = l64.max(axis=1)
+    lp = l64[np.arange(b.N), b.selected] - (top + np.log(np.exp(l64 - top[:, None]).sum(axis=1)))
+    b.logp_old[:] = (lp + 0.05).astype(np.float32)
+    b.logp_ref[:] = (lp - 0.03).astype(np.float32)
+    want = run_oracle(b)
+    assert np.isfinite(want[2]).all()
+    dev = torch.from_numpy(b.padded(50304)).cuda()
+    st = G.grpo_logits_cuda_device_inplace(dev, b.logp_old, b.logp_ref, b.selected, b.advantages, b.mask,
+                                           b.B, b.G, b.T, V, 50304, cfg_of(b))
+    out = dev.cpu().numpy()
+    assert_stats(st, want[0], want[1], "wide range")
+    assert_grad(out[:, :V], want[2], "wide range")
+
+
 def test_config3_full_size():
     # N = 1024 x V = 32768, full mask, token-mean
     b = W.fused_v32k_case(42)
