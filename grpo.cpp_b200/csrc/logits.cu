@@ -35,12 +35,15 @@
 //   (1) evaluate e_i = 2^(x_i*log2e - shift) with a two-constant log2e and one FMA residual so
 //       the exponent itself carries no systematic error,
 //   (2) sum the e_i exactly (compensated fp32 chains, or double), combining per-warp partial
-//       sums with factors computed in double and scaling by the measured mean error of the
+//       sums with factors good to ~5e-9 and scaling by the measured mean error of the
 //       hardware ex2, and
-//   (3) recompute in double the elements that can each carry a visible share of the normaliser
+//   (3) recompute to ~5e-9 the elements that can each carry a visible share of the normaliser
 //       (every thread's two largest in the pipelined kernel; those above 1/256 of it in the
 //       streaming kernel) and correct the sum.
-// The gradient itself only needs the fp32 e_i.
+// The pipelined kernel does (2) and (3) in float-float arithmetic (an fp32 head plus an fp32
+// tail, ~48 bits): double precision gave the same digits but its dependent chains, twice per
+// thread and row, cost a sixth of the kernel's bandwidth.  The streaming kernel, which is not
+// bound by them, uses double.  The gradient itself only needs the fp32 e_i.
 //
 // Neither row kernel touches a masked row's logits or selected id; both write zeros over all P
 // columns of a masked row and over columns [V, P) of an active one.
@@ -365,7 +368,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 // Nothing on a row's critical path is an ordinary global load: such a load queues behind the
 // bulk copies this SM already has in flight and comes back thousands of cycles later.  The
 // per-row scalars are staged per batch of rows, the selected logit is read back from the ring,
-// and the elements that are redone in double are the thread's own two largest chunk maxima.
+// and the elements that are redone accurately are the thread's own two largest chunk maxima.
 // Issuing a bulk copy can itself stall for a long time when the copy queue is full, which is
 // why a dedicated warp does it.
 // ---------------------------------------------------------------------------------------------
@@ -645,7 +648,7 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
             }
 
             // ---- padding columns of the chunk that straddles V, finiteness probe, and the thread's
-            //      two largest chunk maxima (its candidates for the double-precision correction)
+            //      two largest chunk maxima (its candidates for the accurate correction)
             if (special_j >= 0) {  // the one thread that owns the chunk holding column V
 #pragma unroll
                 for (int j = 0; j < VEC; j++) {
@@ -678,7 +681,7 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
 
             // ---- one exp per element relative to the warp's maximum; compensated fp32 sums (four
             //      independent Kahan chains, two per packed instruction) keep the thread's total
-            //      exact to double rounding
+            //      exact to about 48 bits
             const float m_warp = warp_max(m);
             const float shift = (m_warp == kNegInf ? 0.0f : m_warp) * kLog2eHi;
             const float2 neg_shift2 = make_float2(-shift, -shift);
@@ -733,7 +736,7 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
             }
 
             // ---- warp 0 of every CTA combines all partials of the row: same slots, same order,
-            //      same bits in every CTA.  Factors in double, fixed shuffle trees.
+            //      same bits in every CTA.  Factors and sums in float-float, fixed shuffle trees.
             if (warp == 0) {
                 constexpr int PARTS = CLUSTER * WARPS;
                 constexpr int PER_LANE = (PARTS + 31) / 32;
@@ -1154,19 +1157,6 @@ constexpr Variant kVariants[] = {
     {8, 128, 16, 4, 6, "8x128x16"},   // 3: <=  65536   (GPT-2's 50,304)
     {8, 256, 16, 4, 6, "8x256x16"},   // 4: <= 131072   96 KB ring, two CTAs per SM
     {8, 512, 16, 4, 6, "8x512x16"},   // 5: <= 262144   192 KB ring of 32 KB stages, one CTA per SM
-#ifdef GRPO_EXPERIMENT_VARIANTS
-    {8, 128, 16, 4, 6, "8x128x16b3"},
-    {8, 128, 14, 2, 12, "8x128x14"},
-    {8, 256, 8, 2, 6, "8x256x8b3"},
-    {8, 256, 8, 2, 6, "8x256x8b2"},
-    {8, 192, 9, 3, 5, "8x192x9b4"},
-    {8, 192, 9, 3, 5, "8x192x9b3"},
-    {8, 256, 7, 1, 12, "8x256x7b3"},
-    {8, 128, 8, 4, 4, "8x128x8b6"},
-    {8, 128, 8, 4, 4, "8x128x8b5"},
-    {8, 128, 8, 2, 8, "8x128x8t2b6"},
-    {8, 128, 8, 4, 3, "8x128x8s3b7"},
-#endif
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -1229,19 +1219,6 @@ cudaError_t launch_by_index(int variant, const LogitsArgs& a, cudaStream_t strea
         case 3: return launch_variant<128, 16, 4, 6, 8, 4, CHECK>(a, stream);
         case 4: return launch_variant<256, 16, 4, 6, 8, 2, CHECK>(a, stream);
         case 5: return launch_variant<512, 16, 4, 6, 8, 1, CHECK>(a, stream);
-#ifdef GRPO_EXPERIMENT_VARIANTS
-        case 6: return launch_variant<128, 16, 4, 6, 8, 3, CHECK>(a, stream);
-        case 7: return launch_variant<128, 14, 2, 12, 8, 4, CHECK>(a, stream);
-        case 8: return launch_variant<256, 8, 2, 6, 8, 3, CHECK>(a, stream);
-        case 9: return launch_variant<256, 8, 2, 6, 8, 2, CHECK>(a, stream);
-        case 10: return launch_variant<192, 9, 3, 5, 8, 4, CHECK>(a, stream);
-        case 11: return launch_variant<192, 9, 3, 5, 8, 3, CHECK>(a, stream);
-        case 12: return launch_variant<256, 7, 1, 12, 8, 3, CHECK>(a, stream);
-        case 13: return launch_variant<128, 8, 4, 4, 8, 6, CHECK>(a, stream);
-        case 14: return launch_variant<128, 8, 4, 4, 8, 5, CHECK>(a, stream);
-        case 15: return launch_variant<128, 8, 2, 8, 8, 6, CHECK>(a, stream);
-        case 16: return launch_variant<128, 8, 4, 3, 8, 7, CHECK>(a, stream);
-#endif
         default: return cudaErrorInvalidValue;
     }
 }
