@@ -5,14 +5,16 @@
 // (src/cuda/grpo_loss_cuda.cu:181-349).  Two kernels live here.
 //
 // PIPELINED kernel (what GRPO_B200_LOGITS_FUSED runs whenever the layout allows):
-//   * persistent: thread-block clusters of 1/2/4/8 small CTAs (four CTAs of 128 consumer threads
-//     per SM for the common widths, so that one CTA's serial phases overlap the others' work)
-//     walk the rows, every cluster taking every n-th active and every n-th masked row when the
-//     caller supplies the row order, else every n-th row;
+//   * persistent: thread-block clusters of 1/2/4/8 small CTAs (four CTAs of 128 threads and 128
+//     registers per SM for the common widths, so that one CTA's serial phases overlap the
+//     others' work) walk the rows, every cluster taking every n-th active and every n-th masked
+//     row when the caller supplies the row order, else every n-th row;
 //   * a ring of shared-memory stages is filled by bulk asynchronous copies
-//     (cp.async.bulk global -> shared, completion on an mbarrier) issued by a dedicated producer
-//     warp up to STAGES tiles ahead, so the next rows stream in from HBM while the current row is
-//     being reduced and written back -- the copy engine, not thread occupancy, hides latency;
+//     (cp.async.bulk global -> shared, completion on an mbarrier) up to STAGES tiles ahead, so
+//     the next rows stream in from HBM while the current row is being reduced and written back
+//     -- the copy engine, not thread occupancy, hides latency.  One lane of the CTA's last warp
+//     requests them at the points of a row where that warp would otherwise idle; there is no
+//     producer warp, whose registers would cost every other thread a quarter of its own;
 //   * each thread lifts its chunks from the ring into registers (128-bit LDS), releases the
 //     stage, and keeps the row slice in registers until the gradient is stored (128-bit
 //     streaming stores): one HBM read and one HBM write per logit, one exp per element;
@@ -335,7 +337,7 @@ __device__ __forceinline__ void send_part(WarpPart* slot, uint64_t* bar, unsigne
                  : "memory");
 }
 
-// barrier 1: the consumer warps only (the producer warp never joins it)
+// barrier 1: all THREADS threads of the CTA (a named barrier, kept apart from __syncthreads)
 __device__ __forceinline__ void consumer_sync(int threads) {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
@@ -363,22 +365,24 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 // ---------------------------------------------------------------------------------------------
 // Pipelined kernel.  Requires P % 4 == 0 and 16-byte aligned bases; the dispatcher guarantees
 // ceil(P/4 / CLUSTER) <= THREADS * VEC.  TJ chunks per thread per ring stage, STAGES stages.
-// The block has THREADS consumer threads plus one producer warp.
+// The block has THREADS threads; STAGES >= VEC / TJ (a whole row fits the ring).
 //
 // Nothing on a row's critical path is an ordinary global load: such a load queues behind the
 // bulk copies this SM already has in flight and comes back thousands of cycles later.  The
 // per-row scalars are staged per batch of rows, the selected logit is read back from the ring,
 // and the elements that are redone accurately are the thread's own two largest chunk maxima.
 // Issuing a bulk copy can itself stall for a long time when the copy queue is full, which is
-// why a dedicated warp does it.
+// why it is done by a warp that has just handed its partial over and has nothing to do until
+// the row leader is through.
 // ---------------------------------------------------------------------------------------------
 template <int THREADS, int VEC, int TJ, int STAGES, int CLUSTER, int MINB, bool CHECK>
-__global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(const LogitsArgs a) {
+__global__ void __launch_bounds__(THREADS, MINB) logits_pipelined_kernel(const LogitsArgs a) {
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE_CHUNKS = TJ * THREADS;
     constexpr int TILES = VEC / TJ;
     constexpr int BATCH = 128;  // rows whose scalars are staged at once
     static_assert(VEC % TJ == 0, "tiles must cover the per-thread chunks exactly");
+    static_assert(STAGES >= VEC / TJ, "the ring holds at least one whole row slice");
     static_assert(WARPS <= 32, "warp indices fit one lane each");
 
     extern __shared__ __align__(128) unsigned char ring_raw[];
@@ -401,7 +405,6 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    const bool is_producer = warp == WARPS;
     // The reduce kernel that follows in the stream may be made resident as this grid's CTAs retire
     // and run its prologue; it still waits for this whole grid before it reads anything written here.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -429,7 +432,7 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
     // special_j is its register index there, -1 everywhere else.
     const int v_rem = V & 3;
     int special_j = -1;
-    if (v_rem != 0 && !is_producer) {
+    if (v_rem != 0) {
         const int cs = (V >> 2) - c0;
         if (cs >= 0 && cs < n_store && cs % THREADS == tid) special_j = cs / THREADS;
     }
@@ -475,66 +478,48 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
     const int n_mine = order ? mine_active + mine_masked
                              : (cluster_id < n_rows ? (n_rows - cluster_id + n_clusters - 1) / n_clusters : 0);
 
-    unsigned q = 0;     // consumers: tiles consumed; producer: tiles requested
+    unsigned q = 0;     // tiles consumed
     bool alive = true;  // false after a wait timed out: skip the ring, keep meeting barriers
+    // Lane 0 of the last warp requests the tiles, at the two points where that warp has nothing
+    // else to do: when a batch of rows has been staged (it fills the ring) and right after its
+    // hand-over of a row (it refills the stages that row gave back, while warp 0 combines and runs
+    // the leader).  It walks the staged rows of the current batch only, so the ring runs dry at a
+    // batch's end: one memory latency per BATCH rows.
+    const bool is_issuer = warp == WARPS - 1 && lane == 0;
+    int p_slot = 0, p_tile = 0;  // next row of the batch and next tile of it to request
+    unsigned q_prod = 0;         // tiles requested
     unsigned row_parity = 0;
     unsigned xuses[2] = {0u, 0u};
 
-    if (is_producer) {
-        // ---- producer warp: free-running over all of this cluster's rows.  The lanes read 32 rows'
-        //      mask words at a time (one group ahead, so the latency hides behind the group being
-        //      issued); lane 0 requests every tile of every active row, in order, as the ring's
-        //      stages come free.  It shares nothing with the consumers but the ring.
-        if (n_tiles > 0) {
-            // lane l's candidate of the group starting at `base`: the row to load, or -1.  Without a
-            // row order the candidates are this cluster's rows in turn (masked ones give -1); with
-            // one they are its active rows in turn.
-            const int n_cand = order ? mine_active : n_mine;
-            auto group_rows = [&](int base) -> int {
-                const int k = base + lane;
-                if (k >= n_cand) return -1;
-                const size_t at = static_cast<size_t>(cluster_id) + static_cast<size_t>(k) * n_clusters;
-                if (order) {
-                    const int r = active_rows[at];
-                    return r >= 0 && r < n_rows ? r : -1;  // a row index outside the batch is never loaded
-                }
-                return a.mask[at] != 0 ? static_cast<int>(at) : -1;
-            };
-            int next_row = group_rows(0);
-            for (int base = 0; base < n_cand && alive; base += 32) {
-                const int my_row = next_row;
-                if (base + 32 < n_cand) next_row = group_rows(base + 32);
-                unsigned bits = __ballot_sync(0xffffffffu, my_row >= 0);
-                while (bits != 0) {  // uniform: every lane walks the same bits
-                    const int src_lane = __ffs(bits) - 1;
-                    bits &= bits - 1;
-                    const int p_row = __shfl_sync(0xffffffffu, my_row, src_lane);
-                    if (lane == 0 && alive) {
-                        const float* row_src =
-                            a.logits + static_cast<size_t>(p_row) * static_cast<size_t>(a.P) + 4 * static_cast<size_t>(c0);
-                        for (int t = 0; t < n_tiles; t++) {
-                            const unsigned slot = q % STAGES;
-                            const unsigned parity = (q / STAGES) & 1u;
-                            if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
-                                alive = false;
-                                atomicOr(&abort_sh, kStatusPipelineTimeout);
-                                break;
-                            }
-                            const int first = t * TILE_CHUNKS;
-                            const uint32_t bytes = static_cast<uint32_t>(min(TILE_CHUNKS, n_load - first)) * 16u;
-                            mbar_arrive_expect_tx(&full_bar[slot], bytes);
-                            bulk_load(ring + static_cast<size_t>(slot) * TILE_CHUNKS,
-                                      row_src + 4 * static_cast<size_t>(first), bytes, &full_bar[slot]);
-                            q++;
-                        }
-                    }
-                }
-                alive = __shfl_sync(0xffffffffu, static_cast<int>(alive), 0) != 0;  // the loop condition stays uniform
+    // request up to `budget` more tiles of the current batch's active rows, in the order the consumers take them
+    auto issue_tiles = [&](int budget, int batch_rows) {
+        while (budget > 0) {
+            while (p_slot < batch_rows && meta_mask[p_slot] != 1) p_slot++;
+            if (p_slot >= batch_rows) break;
+            const unsigned slot = q_prod % STAGES;
+            const unsigned parity = (q_prod / STAGES) & 1u;
+            if (!mbar_wait(&empty_bar[slot], parity ^ 1u)) {
+                atomicOr(&abort_sh, kStatusPipelineTimeout);
+                p_slot = batch_rows;  // request nothing more: the consumers' waits run out and report
+                break;
+            }
+            const float* row_src = a.logits + static_cast<size_t>(meta_row[p_slot]) * static_cast<size_t>(a.P) +
+                                   4 * static_cast<size_t>(c0);
+            const int first = p_tile * TILE_CHUNKS;
+            const uint32_t bytes = static_cast<uint32_t>(min(TILE_CHUNKS, n_load - first)) * 16u;
+            mbar_arrive_expect_tx(&full_bar[slot], bytes);
+            bulk_load(ring + static_cast<size_t>(slot) * TILE_CHUNKS, row_src + 4 * static_cast<size_t>(first), bytes,
+                      &full_bar[slot]);
+            q_prod++;
+            budget--;
+            if (++p_tile == n_tiles) {
+                p_tile = 0;
+                p_slot++;
             }
         }
-    }
+    };
 
-    for (int batch_first = 0; !is_producer && batch_first < n_mine; batch_first += BATCH) {
+    for (int batch_first = 0; batch_first < n_mine; batch_first += BATCH) {
         const int batch_rows = min(BATCH, n_mine - batch_first);
         consumer_sync(THREADS);  // every consumer is done with the previous batch's scalars
         for (int i = tid; i < batch_rows; i += THREADS) {
@@ -571,13 +556,17 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
             }
         }
         consumer_sync(THREADS);
+        // every tile requested so far has been consumed: the ring is empty and the new batch is staged
+        p_slot = 0;
+        p_tile = 0;
+        if (is_issuer && n_tiles > 0) issue_tiles(STAGES, batch_rows);
 
         // ---- consumer warps
         for (int k_row = 0; k_row < batch_rows; k_row++) {
             const size_t row = static_cast<size_t>(meta_row[k_row]);
             float4* out = reinterpret_cast<float4*>(a.dlogits + row * static_cast<size_t>(a.P)) + c0;
 
-            if (meta_mask[k_row] == 2) continue;  // a row index outside the batch: skipped by producer and consumers alike
+            if (meta_mask[k_row] == 2) continue;  // a row index outside the batch: neither loaded nor stored
             if (meta_mask[k_row] == 0) {  // uniform over the cluster: no barrier is reached
                 const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
@@ -634,7 +623,7 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
                 }
             }
 
-            // ---- the row's stages go back to the producer; the next rows' tiles start streaming now
+            // ---- the row's stages are free again; the issuing lane refills them after the hand-over below
             __syncwarp();
             if (lane == 0) {
 #pragma unroll
@@ -734,6 +723,8 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
                     send_part(&parts[row_parity][crank * WARPS + warp], &xbar[row_parity], static_cast<unsigned>(lane),
                               s_warp, m_warp, shift, chk, xs0, hs0);
             }
+
+            if (is_issuer && n_tiles > 0) issue_tiles(n_tiles, batch_rows);  // the stages this row gave back
 
             // ---- warp 0 of every CTA combines all partials of the row: same slots, same order,
             //      same bits in every CTA.  Factors and sums in float-float, fixed shuffle trees.
@@ -840,9 +831,9 @@ __global__ void __launch_bounds__(THREADS + 32, MINB) logits_pipelined_kernel(co
     if (tid == 0) q_cons_final = q;
     if (!alive) atomicOr(&abort_sh, kStatusPipelineTimeout);
     __syncthreads();
-    if (is_producer && lane == 0) {
+    if (is_issuer) {
         unsigned qc = q_cons_final;
-        while (qc < q) {  // requested but never consumed (only after a timeout)
+        while (qc < q_prod) {  // requested but never consumed (only after a timeout)
             mbar_wait(&full_bar[qc % STAGES], (qc / STAGES) & 1u);
             qc++;
         }
@@ -1173,7 +1164,7 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
 
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(THREADS + 32, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = ring_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -1194,7 +1185,7 @@ cudaError_t launch_variant(const LogitsArgs& a, cudaStream_t stream) {
         if (CLUSTER == 1) {
             // plain launch: every SM takes CTAs independently
             int per_sm = 0;
-            err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS + 32, ring_bytes);
+            err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, ring_bytes);
             if (err != cudaSuccess) return err;
             max_clusters = per_sm * sms;
         } else {

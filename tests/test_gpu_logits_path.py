@@ -5,6 +5,7 @@ terms within 1e-5 relative; dL/dlogits within 1e-7 + 1e-5 * |want|; valid-token 
 padded tail columns and masked rows exactly zero.
 """
 import os
+import re
 import subprocess
 
 import numpy as np
@@ -137,7 +138,7 @@ def test_every_resident_variant_matches_oracle():
     names = D.variants()
     try:
         for idx, name in enumerate(names):
-            c, t, v = (int("".join(ch for ch in x if ch.isdigit())) for x in name.split("x"))
+            c, t, v = (int(x) for x in re.match(r"(\d+)x(\d+)x(\d+)", name).groups())
             cap = c * t * v * 4
             V = cap - 37 if cap > 2048 else cap - 5
             P = cap
