@@ -538,15 +538,26 @@ __global__ void __launch_bounds__(THREADS, MINB) logits_pipelined_kernel(const L
                     r = 0;
                     atomicOr(&abort_sh, kStatusRowOrderMismatch);
                 } else {
-                    r = static_cast<size_t>(listed);
-                    if ((a.mask[r] != 0) != (mk != 0)) atomicOr(&abort_sh, kStatusRowOrderMismatch);
+                    r = static_cast<size_t>(listed);  // checked against the mask below, off the path to the first request
                 }
             } else {
                 mk = a.mask[r] != 0;
             }
             meta_row[i] = static_cast<int>(r);
             meta_mask[i] = static_cast<unsigned char>(mk);
-            if (mk == 1) {
+        }
+        consumer_sync(THREADS);
+        // Every tile requested so far has been consumed: the ring is empty, and the new batch's rows
+        // are known.  The first tiles are requested now, so that they travel while the rows' scalars
+        // are being fetched.
+        p_slot = 0;
+        p_tile = 0;
+        if (is_issuer && n_tiles > 0) issue_tiles(STAGES, batch_rows);
+        for (int i = tid; i < batch_rows; i += THREADS) {
+            if (order && meta_mask[i] != 2 && (a.mask[meta_row[i]] != 0) != (meta_mask[i] != 0))
+                atomicOr(&abort_sh, kStatusRowOrderMismatch);
+            if (meta_mask[i] == 1) {
+                const size_t r = static_cast<size_t>(meta_row[i]);
                 const long long seq = (a.row_offset + static_cast<long long>(r)) / a.tokens_per_seq;
                 meta_sel[i] = a.selected[r];
                 meta_old[i] = a.logp_old[r];
@@ -556,10 +567,6 @@ __global__ void __launch_bounds__(THREADS, MINB) logits_pipelined_kernel(const L
             }
         }
         consumer_sync(THREADS);
-        // every tile requested so far has been consumed: the ring is empty and the new batch is staged
-        p_slot = 0;
-        p_tile = 0;
-        if (is_issuer && n_tiles > 0) issue_tiles(STAGES, batch_rows);
 
         // ---- consumer warps
         for (int k_row = 0; k_row < batch_rows; k_row++) {
