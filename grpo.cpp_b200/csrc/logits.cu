@@ -337,6 +337,13 @@ __device__ __forceinline__ void send_part(WarpPart* slot, uint64_t* bar, unsigne
                  : "memory");
 }
 
+// 32 bytes of zeros with one store (256-bit stores, sm_100), marked for early eviction from L2.
+// The address must be 32-byte aligned.
+__device__ __forceinline__ void store_zero32(float4* p) {
+    const float z = 0.0f;
+    asm volatile("st.global.L2::evict_first.v8.f32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"l"(p), "f"(z) : "memory");
+}
+
 // barrier 1: all THREADS threads of the CTA (a named barrier, kept apart from __syncthreads)
 __device__ __forceinline__ void consumer_sync(int threads) {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
@@ -415,6 +422,13 @@ __global__ void __launch_bounds__(THREADS, MINB) logits_pipelined_kernel(const L
         *a.status = 0;
         *a.counter = 0u;
     }
+    // the row order's two counts, requested now so that their latency overlaps the start-up barriers below
+    const int* order = a.row_order;
+    int order_active = 0, order_masked = 0;
+    if (order) {
+        order_active = __ldg(order);
+        order_masked = __ldg(order + 1);
+    }
     unsigned crank = 0;
     if (CLUSTER > 1) crank = cg::this_cluster().block_rank();
     const int cluster_id = blockIdx.x / CLUSTER;
@@ -428,6 +442,8 @@ __global__ void __launch_bounds__(THREADS, MINB) logits_pipelined_kernel(const L
     const int n_store = max(min(c0 + per_cta, P4) - c0, 0);  // chunks of the slice (stores)
     const int n_load = max(min(c0 + n_store, (V + 3) >> 2) - c0, 0);  // chunks that hold vocabulary (loads)
     const int n_tiles = (n_load + TILE_CHUNKS - 1) / TILE_CHUNKS;
+    // masked rows are zero-filled with 256-bit stores when every row's slice starts on a 32-byte boundary
+    const bool wide_fill = (a.P & 7) == 0 && (c0 & 1) == 0 && (reinterpret_cast<uintptr_t>(a.dlogits) & 31u) == 0;
     // The single chunk that straddles column V (when V % 4 != 0) belongs to one thread of one CTA:
     // special_j is its register index there, -1 everywhere else.
     const int v_rem = V & 3;
@@ -461,16 +477,15 @@ __global__ void __launch_bounds__(THREADS, MINB) logits_pipelined_kernel(const L
     // the active rows' phases.
     // A row order whose two counts do not add up to the row count belongs to another batch: it is
     // ignored (every CTA reads the same two words, so the decision is uniform) and the pass reports it.
-    const int* order = a.row_order;
     if (order) {
-        const int na = order[0], nm = order[1];
+        const int na = order_active, nm = order_masked;
         if (na < 0 || nm < 0 || static_cast<long long>(na) + nm != a.n_rows) {
             order = nullptr;
             if (blockIdx.x == 0 && tid == 0) atomicOr(&abort_sh, kStatusRowOrderMismatch);
         }
     }
-    const int total_active = order ? order[0] : 0;
-    const int total_masked = order ? order[1] : 0;
+    const int total_active = order ? order_active : 0;
+    const int total_masked = order ? order_masked : 0;
     const int* active_rows = order ? order + 2 : nullptr;
     const int* masked_rows = order ? order + 2 + total_active : nullptr;
     const int mine_active = order && cluster_id < total_active ? (total_active - cluster_id + n_clusters - 1) / n_clusters : 0;
@@ -576,10 +591,20 @@ __global__ void __launch_bounds__(THREADS, MINB) logits_pipelined_kernel(const L
             if (meta_mask[k_row] == 2) continue;  // a row index outside the batch: neither loaded nor stored
             if (meta_mask[k_row] == 0) {  // uniform over the cluster: no barrier is reached
                 const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (wide_fill) {
+                    const int pairs = n_store >> 1;
 #pragma unroll
-                for (int j = 0; j < VEC; j++) {
-                    const int local = j * THREADS + tid;
-                    if (local < n_store) store_stream(out + local, zero);
+                    for (int j = 0; j < VEC / 2; j++) {
+                        const int local = j * THREADS + tid;
+                        if (local < pairs) store_zero32(out + 2 * local);
+                    }
+                    if ((n_store & 1) && tid == 0) store_stream(out + n_store - 1, zero);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) {
+                        const int local = j * THREADS + tid;
+                        if (local < n_store) store_stream(out + local, zero);
+                    }
                 }
                 continue;
             }

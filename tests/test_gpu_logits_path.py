@@ -105,6 +105,37 @@ def test_masked_rows_are_never_read():
         assert_grad(out, want[2])
 
 
+@pytest.mark.parametrize("V,P,offset_floats", [
+    (1021, 1024, 0),     # rows on 32-byte boundaries: masked rows are filled with 256-bit stores
+    (1021, 1024, 4),     # the same rows starting 16 bytes off a 32-byte boundary: 128-bit stores
+    (1017, 1020, 0),     # a row pitch that is a multiple of 16 bytes only
+    (50257, 50304, 0),   # the benchmark's shape: cluster of eight, slices of an even number of chunks
+    (50257, 50308, 0),   # slices of an odd number of chunks
+    (40000, 40024, 4),
+])
+def test_masked_row_fill_alignments(V, P, offset_floats):
+    """Masked rows come back as exact zeros over all P columns, and nothing is written outside the
+    batch's rows, for every alignment of the row base and pitch (the zero fill picks its store width
+    by them).  The rows around the batch are sentinels."""
+    import torch
+    b = W.logits_case(2, 2, 5, V, min_len=1, reduction=W.TOKEN_MEAN, seed=V + P + offset_floats)
+    want = run_oracle(b)
+    guard = 64
+    flat = torch.full((offset_floats + guard + b.N * P + guard,), 7.25, dtype=torch.float32, device="cuda")
+    rows = flat[offset_floats + guard: offset_floats + guard + b.N * P].view(b.N, P)
+    padded = b.padded(P)
+    padded[b.mask == 0] = np.nan
+    rows.copy_(torch.from_numpy(padded))
+    st = G.grpo_logits_cuda_device_inplace(rows, b.logp_old, b.logp_ref, b.selected, b.advantages, b.mask,
+                                           b.B, b.G, b.T, V, P, cfg_of(b))
+    out = rows.cpu().numpy()
+    assert_stats(st, want[0], want[1])
+    assert_grad(out[:, :V], want[2])
+    assert (out[b.mask == 0] == 0).all() and (out[:, V:] == 0).all()
+    edge = flat.cpu().numpy()
+    assert (edge[: offset_floats + guard] == 7.25).all() and (edge[offset_floats + guard + b.N * P:] == 7.25).all()
+
+
 @pytest.mark.parametrize("call,msg", [
     (lambda b: G.grpo_logits_cuda(b.logits, b.logp_old, b.logp_ref, np.where(b.mask == 1, b.V, -1), b.advantages,
                                   b.mask, b.B, b.G, b.T, b.V), "selected token is outside the vocabulary"),
