@@ -194,7 +194,7 @@ int grpo_b200_loss(const float* logp_new, const float* logp_old, const float* lo
 
 size_t grpo_b200_logits_workspace_bytes(int64_t n_rows) {
     // one 32-byte record per row, one 32-byte slot for the status word and the ticket counter,
-    // then five doubles per block of 256 rows for the reduce kernel
+    // then room for five doubles per 256 rows for the reduce kernel (it uses one slot per block of 1,024 rows)
     if (n_rows <= 0) return 0;
     const size_t blocks = (static_cast<size_t>(n_rows) + 255) / 256;
     return static_cast<size_t>(n_rows) * sizeof(RowRecord) + 32 + blocks * 5 * sizeof(double);

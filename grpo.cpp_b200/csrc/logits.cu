@@ -1005,7 +1005,7 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
 //    the next pass's weights from the global counts.  A non-zero
 //    status word (a pipeline wait timed out) turns bad_inputs into -1, an exchange that timed
 //    out into -2.
-constexpr int kReduceThreads = 256;
+constexpr int kReduceThreads = 1024;
 
 __device__ __forceinline__ unsigned long long* exchange_slot(unsigned char* region, long long stride, int buf, int src) {
     return reinterpret_cast<unsigned long long*>(region + kExchangeHeaderBytes) + (buf * kExchangeMaxWorld + src) * stride * 2;
@@ -1061,23 +1061,31 @@ __global__ void __launch_bounds__(kReduceThreads) logits_reduce_kernel(const Log
         if (a.selected_logp) a.selected_logp[row] = lp_new;
     }
     block_sum<kReduceThreads, 5>(v, scratch);
-    if (tid == 0) {
-#pragma unroll
-        for (int k = 0; k < 5; k++) a.partials[static_cast<size_t>(blockIdx.x) * 5 + k] = v[k];
-        __threadfence();  // the slot and this block's counts are visible before the ticket is taken
-        is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
-        timed_out = 0;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-
     double t[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
-    for (unsigned b = tid; b < gridDim.x; b += kReduceThreads) {
+    if (gridDim.x == 1) {
+        // a launch of one block (up to 1,024 rows) has its totals already: no slot, no ticket, no second
+        // round trip through memory -- the same bits as the general path gives for one slot
+        if (tid == 0) timed_out = 0;
 #pragma unroll
-        for (int k = 0; k < 5; k++) t[k] += __ldcg(a.partials + static_cast<size_t>(b) * 5 + k);
+        for (int k = 0; k < 5; k++) t[k] = v[k] + 0.0;  // as the general path's additions of zero leave it (-0 becomes +0)
+        __syncthreads();
+    } else {
+        if (tid == 0) {
+#pragma unroll
+            for (int k = 0; k < 5; k++) a.partials[static_cast<size_t>(blockIdx.x) * 5 + k] = v[k];
+            __threadfence();  // the slot and this block's counts are visible before the ticket is taken
+            is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+            timed_out = 0;
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        for (unsigned b = tid; b < gridDim.x; b += kReduceThreads) {
+#pragma unroll
+            for (int k = 0; k < 5; k++) t[k] += __ldcg(a.partials + static_cast<size_t>(b) * 5 + k);
+        }
+        block_sum<kReduceThreads, 5>(t, scratch);
     }
-    block_sum<kReduceThreads, 5>(t, scratch);
     if (tid == 0) {
         const int status = *a.status;
         if (status & kStatusRowOrderMismatch) t[4] = kBadInputsRowOrder;
