@@ -177,16 +177,21 @@ int check_options(const Options& o) {
 
 // Token-array checks shared by all three calls.  logp_new is null for the logits calls, whose
 // reference validators pass a zero vector of the right size in its place.
-int validate_inputs(const float* lp_new, size_t n_new, const float* lp_old, size_t n_old, const float* lp_ref,
-                    size_t n_ref, const float* adv, size_t n_adv, const int32_t* mask, size_t n_mask,
-                    const Shape& shape, const Options& opt) {
+int validate_sizes(bool has_new, size_t n_new, size_t n_old, size_t n_ref, size_t n_adv, size_t n_mask,
+                   const Shape& shape, const Options& opt) {
     if (int rc = check_options(opt)) return rc;
-    if (lp_new)
+    if (has_new)
         if (int rc = expect_size("logp_new", n_new, shape.tokens)) return rc;
     if (int rc = expect_size("logp_old", n_old, shape.tokens)) return rc;
     if (int rc = expect_size("logp_ref", n_ref, shape.tokens)) return rc;
     if (int rc = expect_size("advantages", n_adv, shape.sequences)) return rc;
-    if (int rc = expect_size("mask", n_mask, shape.tokens)) return rc;
+    return expect_size("mask", n_mask, shape.tokens);
+}
+
+int validate_inputs(const float* lp_new, size_t n_new, const float* lp_old, size_t n_old, const float* lp_ref,
+                    size_t n_ref, const float* adv, size_t n_adv, const int32_t* mask, size_t n_mask,
+                    const Shape& shape, const Options& opt) {
+    if (int rc = validate_sizes(lp_new != nullptr, n_new, n_old, n_ref, n_adv, n_mask, shape, opt)) return rc;
     // one branch-free sweep first (it vectorises); only a batch that has a bad value is walked again in the
     // reference's order to find which complaint comes first
     unsigned bad = 0;
@@ -215,6 +220,8 @@ int validate_inputs(const float* lp_new, size_t n_new, const float* lp_old, size
 }  // namespace host
 namespace {
 // Host twin of make_weights (src/cuda/grpo_loss_cuda.cu:21-57): same fp32 expressions.
+int weights_from_lengths(const int* lengths, int valid_tokens, const Shape& shape, const Options& opt, float* weights);
+
 int make_weights(const int32_t* mask, const Shape& shape, int T, const Options& opt, float* weights,
                  int& valid_tokens) {
     std::vector<int> lengths(shape.sequences, 0);
@@ -226,6 +233,10 @@ int make_weights(const int32_t* mask, const Shape& shape, int T, const Options& 
         lengths[s] = count;
         valid_tokens += count;
     }
+    return weights_from_lengths(lengths.data(), valid_tokens, shape, opt, weights);
+}
+
+int weights_from_lengths(const int* lengths, int valid_tokens, const Shape& shape, const Options& opt, float* weights) {
     const float n_seq = static_cast<float>(shape.sequences);
     for (size_t s = 0; s < shape.sequences; s++) {
         if (lengths[s] == 0) return invalid("every sequence needs at least one valid token");
@@ -344,6 +355,107 @@ cudaError_t stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, cons
     return err;
 }
 
+// copy n words and report whether any of them is an infinity or a NaN (one vectorised loop)
+unsigned copy_and_check_finite(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, size_t n) {
+    unsigned bad = 0;
+    for (size_t i = 0; i < n; i++) {
+        const uint32_t b = src[i];
+        bad |= (b & 0x7f800000u) == 0x7f800000u;
+        dst[i] = b;
+    }
+    return bad;
+}
+// copy the selected ids and report whether an active row's id lies outside [0, V)
+unsigned copy_and_check_selected(const int32_t* __restrict__ sel, const int32_t* __restrict__ mask,
+                                 int32_t* __restrict__ dst, size_t n, uint32_t vocab) {
+    unsigned bad = 0;
+    for (size_t i = 0; i < n; i++) {
+        const int32_t v = sel[i];
+        bad |= (mask[i] != 0) & (static_cast<uint32_t>(v) >= vocab);
+        dst[i] = v;
+    }
+    return bad;
+}
+// copy one response's mask, count its valid tokens and report values outside {0, 1}
+unsigned copy_and_count_mask(const int32_t* __restrict__ src, int32_t* __restrict__ dst, int T, int& count) {
+    unsigned bad = 0;
+    int c = 0;
+    for (int t = 0; t < T; t++) {
+        const int32_t v = src[t];
+        bad |= static_cast<uint32_t>(v) > 1u;
+        c += v != 0;
+        dst[t] = v;
+    }
+    count = c;
+    return bad;
+}
+
+// The in-place call's checks and staging in two sweeps over the host arrays instead of five, with
+// the uploads in flight while the host is still sweeping:
+//   sweep 1  the mask: values in {0, 1}, the responses' valid-token counts, its pinned image; the
+//            mask is uploaded and the row order is built on the device behind it;
+//   sweep 2  log-probabilities finite, selected ids in range on active rows, their pinned images;
+//            then advantages and weights, and the second upload.
+// Whenever a sweep finds something wrong the ordered validators are asked which complaint the
+// reference would raise first (src/cuda/grpo_loss_cuda.cu:584-618, 676-697).  Nothing that was
+// enqueued by then touches the caller's logits.
+int check_and_stage_logits_meta(Arena& arena, Bump& bump, const Shape& shape, int T, int V, int kernel,
+                                const Options& opt, const float* lp_old, size_t n_old, const float* lp_ref,
+                                size_t n_ref, const int32_t* selected, const float* adv, size_t n_adv,
+                                const int32_t* mask, size_t n_mask, LogitsMeta& m, int& valid_tokens) {
+    if (int rc = validate_sizes(false, 0, n_old, n_ref, n_adv, n_mask, shape, opt)) return rc;
+    const size_t n = shape.tokens, s = shape.sequences;
+    char* dev_start = bump.base + bump.off;
+    m.mask_d = bump.take<int32_t>(n);  // first: it travels alone, ahead of the rest
+    char* rest_start = bump.base + bump.off;
+    m.old_d = bump.take<float>(n);
+    m.ref_d = bump.take<float>(n);
+    m.sel_d = bump.take<int32_t>(n);
+    m.adv_d = bump.take<float>(s);
+    m.w_d = bump.take<float>(s);
+    const size_t packed = static_cast<size_t>(bump.base + bump.off - dev_start);
+    const size_t mask_bytes = static_cast<size_t>(rest_start - dev_start);
+    m.order_d = bump.take<int32_t>(grpo_b200_row_order_bytes(static_cast<int64_t>(n)) / sizeof(int32_t));
+    m.result_d = bump.take<grpo_b200_result_t>(1);
+    m.work_bytes = grpo_b200_logits_workspace_bytes(static_cast<int64_t>(n));
+    m.work_d = bump.take<char>(m.work_bytes);
+    char* h = arena.pinned;
+    m.result_h = reinterpret_cast<grpo_b200_result_t*>(h + slice(packed));
+    auto host_of = [&](const void* dev_ptr) { return h + (static_cast<const char*>(dev_ptr) - dev_start); };
+
+    // ---- sweep 1: the mask
+    std::vector<int> lengths(s);
+    int32_t* mask_h = reinterpret_cast<int32_t*>(host_of(m.mask_d));
+    unsigned bad = 0;
+    valid_tokens = 0;
+    for (size_t q = 0; q < s; q++) {
+        int count = 0;
+        bad |= copy_and_count_mask(mask + q * static_cast<size_t>(T), mask_h + q * static_cast<size_t>(T), T, count);
+        lengths[q] = count;
+        valid_tokens += count;
+    }
+    GRPO_CUDA_TRY(cudaMemcpyAsync(dev_start, h, mask_bytes, cudaMemcpyHostToDevice, nullptr));
+    GRPO_CUDA_TRY(launch_row_order(m.mask_d, static_cast<long long>(n), m.order_d, nullptr));
+
+    // ---- sweep 2: log-probabilities, selected ids, advantages (one vectorised copy-and-check loop per array)
+    bad |= copy_and_check_finite(reinterpret_cast<const uint32_t*>(lp_old), reinterpret_cast<uint32_t*>(host_of(m.old_d)), n);
+    bad |= copy_and_check_finite(reinterpret_cast<const uint32_t*>(lp_ref), reinterpret_cast<uint32_t*>(host_of(m.ref_d)), n);
+    bad |= copy_and_check_selected(selected, mask, reinterpret_cast<int32_t*>(host_of(m.sel_d)), n, static_cast<uint32_t>(V));
+    bad |= copy_and_check_finite(reinterpret_cast<const uint32_t*>(adv), reinterpret_cast<uint32_t*>(host_of(m.adv_d)), s);
+    if (bad) {  // which complaint comes first
+        if (int rc = validate_inputs(nullptr, 0, lp_old, n_old, lp_ref, n_ref, adv, n_adv, mask, n_mask, shape, opt))
+            return rc;
+        size_t first_bad;
+        if (check_selected(selected, mask, n, V, first_bad)) return invalid("selected token is outside the vocabulary");
+    }
+    if (kernel != GRPO_B200_LOGITS_SEPARATE && kernel != GRPO_B200_LOGITS_FUSED)
+        return invalid("unknown logits kernel selector");
+    if (int rc = weights_from_lengths(lengths.data(), valid_tokens, shape, opt, reinterpret_cast<float*>(host_of(m.w_d))))
+        return rc;
+    GRPO_CUDA_TRY(cudaMemcpyAsync(rest_start, h + mask_bytes, packed - mask_bytes, cudaMemcpyHostToDevice, nullptr));
+    return GRPO_B200_OK;
+}
+
 }  // namespace
 }  // namespace grpo_b200
 
@@ -422,17 +534,7 @@ int grpo_b200_logits_device_inplace_host(float* logits_and_dlogits, const float*
     if (V <= 0) return invalid("V must be positive");
     if (int rc = expect_size("selected_tokens", n_selected, shape.tokens)) return rc;
     const Options opt{clip_eps, beta, length_alpha, reduction};
-    if (int rc = validate_inputs(nullptr, 0, logp_old, n_logp_old, logp_ref, n_logp_ref, advantages,
-                                 n_advantages, mask, n_mask, shape, opt))
-        return rc;
-    size_t first_bad;
-    if (check_selected(selected, mask, shape.tokens, V, first_bad))
-        return invalid("selected token is outside the vocabulary");
-    if (kernel != GRPO_B200_LOGITS_SEPARATE && kernel != GRPO_B200_LOGITS_FUSED)
-        return invalid("unknown logits kernel selector");
-    std::vector<float> weights(shape.sequences);
-    int valid = 0;
-    if (int rc = make_weights(mask, shape, T, opt, weights.data(), valid)) return rc;
+    if (int rc = check_options(opt)) return rc;  // before any memory is leased, as the other entries do
 
     Lease lease;
     GRPO_CUDA_TRY(lease.acquire());
@@ -441,8 +543,10 @@ int grpo_b200_logits_device_inplace_host(float* logits_and_dlogits, const float*
     GRPO_CUDA_TRY(arena.reserve(meta, meta));
     Bump bump(arena.dev);
     LogitsMeta m;
-    GRPO_CUDA_TRY(stage_logits_meta(arena, bump, shape, logp_old, logp_ref, selected, advantages, weights.data(),
-                                    mask, m, /*order_on_device=*/true));
+    int valid = 0;
+    if (int rc = check_and_stage_logits_meta(arena, bump, shape, T, V, kernel, opt, logp_old, n_logp_old, logp_ref,
+                                             n_logp_ref, selected, advantages, n_advantages, mask, n_mask, m, valid))
+        return rc;
     if (int rc = grpo_b200_logits(logits_and_dlogits, logits_and_dlogits, m.old_d, m.ref_d, m.sel_d, m.adv_d,
                                   m.w_d, m.mask_d, static_cast<int64_t>(shape.tokens), 0, T, V, P, clip_eps, beta,
                                   kernel, 0, nullptr, m.order_d, m.result_d, m.work_d, m.work_bytes, nullptr))

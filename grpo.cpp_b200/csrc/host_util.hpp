@@ -25,6 +25,9 @@ int nonfinite(const char* msg);
 int checked_shape(int B, int G, int T, Shape& out);
 int expect_size(const char* name, size_t got, size_t want);
 int check_options(const Options& o);
+// options, then the sizes of the token arrays, in the reference's order (the first part of validate_inputs)
+int validate_sizes(bool has_new, size_t n_new, size_t n_old, size_t n_ref, size_t n_adv, size_t n_mask,
+                   const Shape& shape, const Options& opt);
 // token-array checks; logp_new may be null (the logits calls have none)
 int validate_inputs(const float* lp_new, size_t n_new, const float* lp_old, size_t n_old, const float* lp_ref,
                     size_t n_ref, const float* adv, size_t n_adv, const int32_t* mask, size_t n_mask,
