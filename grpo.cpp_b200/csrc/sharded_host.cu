@@ -225,24 +225,27 @@ int grpo_b200_logits_sharded_host(grpo_b200_shard_t s, float* logits_and_dlogits
     shape.tokens = n;
     const Options opt{clip_eps, beta, length_alpha, reduction};
     if (reduction < GRPO_B200_SEQUENCE_MEAN || reduction > GRPO_B200_LENGTH_WEIGHTED) return invalid("unknown reduction mode");
-    if (int rc = validate_inputs(nullptr, 0, logp_old, n_logp_old, logp_ref, n_logp_ref, advantages, n_advantages, mask,
-                                 n_mask, shape, opt))
-        return rc;
-    size_t first_bad;
-    if (check_selected(selected, mask, n, s->V, first_bad)) return invalid("selected token is outside the vocabulary");
+    if (int rc = validate_sizes(false, 0, n_logp_old, n_logp_ref, n_advantages, n_mask, shape, opt)) return rc;
+    // the checks and the pinned image of the one packed upload in a single vectorised pass per array; when a
+    // pass finds something wrong the ordered validators say which complaint the reference would raise first
+    char* h = s->pinned;
+    auto host_of = [&](const void* dev_ptr) { return h + (static_cast<const char*>(dev_ptr) - s->dev); };
+    unsigned bad = 0;
+    int local_valid = 0;
+    bad |= copy_and_count_mask(mask, reinterpret_cast<int32_t*>(host_of(s->mask_d)), static_cast<int>(n), local_valid);
+    bad |= copy_and_check_finite(reinterpret_cast<const uint32_t*>(logp_old), reinterpret_cast<uint32_t*>(host_of(s->old_d)), n);
+    bad |= copy_and_check_finite(reinterpret_cast<const uint32_t*>(logp_ref), reinterpret_cast<uint32_t*>(host_of(s->ref_d)), n);
+    bad |= copy_and_check_selected(selected, mask, reinterpret_cast<int32_t*>(host_of(s->sel_d)), n, static_cast<uint32_t>(s->V));
+    bad |= copy_and_check_finite(reinterpret_cast<const uint32_t*>(advantages), reinterpret_cast<uint32_t*>(host_of(s->adv_d)), S);
+    if (bad) {
+        if (int rc = validate_inputs(nullptr, 0, logp_old, n_logp_old, logp_ref, n_logp_ref, advantages, n_advantages, mask,
+                                     n_mask, shape, opt))
+            return rc;
+        size_t first_bad;
+        if (check_selected(selected, mask, n, s->V, first_bad)) return invalid("selected token is outside the vocabulary");
+    }
     if (kernel != GRPO_B200_LOGITS_SEPARATE && kernel != GRPO_B200_LOGITS_FUSED)
         return invalid("unknown logits kernel selector");
-
-    // one packed upload
-    char* h = s->pinned;
-    auto put = [&](const void* src, size_t bytes, const void* dev_ptr) {
-        std::memcpy(h + (static_cast<const char*>(dev_ptr) - s->dev), src, bytes);
-    };
-    put(logp_old, n * 4, s->old_d);
-    put(logp_ref, n * 4, s->ref_d);
-    put(selected, n * 4, s->sel_d);
-    put(mask, n * 4, s->mask_d);
-    put(advantages, S * 4, s->adv_d);
     GRPO_CUDA_TRY(cudaMemcpyAsync(s->dev, h, s->packed_bytes, cudaMemcpyHostToDevice, s->stream));
 
     auto* rb_d = reinterpret_cast<Readback*>(s->readback_d);
