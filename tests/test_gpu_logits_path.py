@@ -189,6 +189,39 @@ def test_every_resident_variant_matches_oracle():
         D.set_variant(-1)
 
 
+def test_variants_with_idle_ctas_and_rows_beyond_one_batch():
+    """Each cluster shape forced onto rows much narrower than it holds, so that the cluster's last
+    CTAs own padding only or nothing at all, on a batch long enough that every cluster stages its
+    rows in more than one round (more than 128 rows per cluster), with masked rows in between."""
+    import torch
+    from grpo_cpp_b200 import device as D
+    names = D.variants()
+    try:
+        for idx, name in enumerate(names):
+            c, t, v = (int(x) for x in re.match(r"(\d+)x(\d+)x(\d+)", name).groups())
+            if c == 1:
+                continue
+            cap = c * t * v * 4
+            V = cap // 16 - 3       # a sixteenth of the cluster has columns
+            P = cap // 8            # an eighth of it has something to store
+            # 74 clusters of eight 128-thread CTAs fit the GPU at once: 12,000 rows are more than 128 per cluster
+            long_batch = c == 8 and t == 128
+            b = W.logits_case(2, 20 if long_batch else 4, 300 if long_batch else 30, V, sigma=2.0, min_len=10,
+                              reduction=W.TOKEN_MEAN, seed=300 + idx)
+            want = run_oracle(b)
+            D.set_variant(idx)
+            dev = torch.from_numpy(b.padded(P)).cuda()
+            assert D.plan(dev, V) == name
+            st = G.grpo_logits_cuda_device_inplace(dev, b.logp_old, b.logp_ref, b.selected, b.advantages, b.mask,
+                                                   b.B, b.G, b.T, V, P, cfg_of(b))
+            out = dev.cpu().numpy()
+            assert_stats(st, want[0], want[1], name)
+            assert_grad(out[:, :V], want[2], name)
+            assert (out[:, V:] == 0).all() and (out[b.mask == 0] == 0).all(), name
+    finally:
+        D.set_variant(-1)
+
+
 def test_wide_dynamic_range_rows():
     """Rows whose logits span far more than a float exponent range in e-folds: a few columns near
     the top and everything else one or two thousand below, inside one thread's chunks, inside one
