@@ -992,7 +992,8 @@ __global__ void __launch_bounds__(kStreamThreads) logits_streaming_kernel(const 
 //
 // 1. One thread per row redoes the row's scalar step in double -- log-sum-exp, log p(selected)
 //    rounded to fp32 exactly as the reference rounds it, the two exponentials -- and each block of
-//    256 rows leaves its five sums (fixed tree) in its own slot of the workspace.  Sharded runs:
+//    1,024 rows leaves its five sums (fixed tree) in its own slot of the workspace (a launch of a
+//    single block keeps them in registers and skips step 2's round trip).  Sharded runs:
 //    the same threads count the next pass's valid tokens per response (integer atomics: exact,
 //    so order does not matter) into the rank's exchange region.
 // 2. The block that finishes last (a ticket counter; no floating-point atomics anywhere) adds the
