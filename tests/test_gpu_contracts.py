@@ -197,3 +197,58 @@ def test_synthetic_logits_have_the_stated_distribution():
     x = W.synthetic_logits_rows(np.arange(64), 50257, 50304, W.synthetic_scale(3.0), 99)
     assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 3.0) < 0.01
     assert 4.0 * 3.0 < float(np.abs(x).max()) <= 4.9 * 3.0
+
+
+def _message(call):
+    try:
+        call()
+    except RuntimeError as e:
+        return str(e)
+    return None
+
+
+def test_in_place_entry_raises_the_complaint_the_ordered_checks_raise():
+    """The in-place entry checks its metadata in fused copy-and-check sweeps; whenever several things are
+    wrong at once it must still name the complaint that comes first in the reference's order
+    (src/cuda/grpo_loss_cuda.cu:584-618, 676-697, 44-46) -- the one the host-vector entry, which walks
+    the arrays in that order, raises for the same inputs.  The device logits must stay untouched."""
+    import torch
+    b = W.logits_case(2, 2, 6, 257, sigma=1.5, min_len=2, seed=73)
+    cfg = cfg_of(b)
+    clean = b.padded(260)
+
+    def both(**changed):
+        args = dict(old=b.logp_old.copy(), ref=b.logp_ref.copy(), sel=b.selected.copy(), adv=b.advantages.copy(),
+                    mask=b.mask.copy(), cfg=cfg, kernel=G.CudaLogitsKernel.fused)
+        args.update(changed)
+        dev = torch.from_numpy(clean.copy()).cuda()
+        inplace = _message(lambda: G.grpo_logits_cuda_device_inplace(dev, args["old"], args["ref"], args["sel"], args["adv"],
+                                                                     args["mask"], b.B, b.G, b.T, b.V, 260, args["cfg"],
+                                                                     args["kernel"]))
+        vectors = _message(lambda: G.grpo_logits_cuda(b.logits, args["old"], args["ref"], args["sel"], args["adv"],
+                                                      args["mask"], b.B, b.G, b.T, b.V, args["cfg"], args["kernel"]))
+        assert inplace == vectors and inplace is not None, (changed.keys(), inplace, vectors)
+        assert (dev.cpu().numpy() == clean).all(), "a rejected call must leave the logits as they were"
+        return inplace
+
+    def poke(a, i, v):
+        a = a.copy()
+        a[i] = v
+        return a
+
+    active = int(np.flatnonzero(b.mask == 1)[3])
+    assert "finite" in both(old=poke(b.logp_old, 5, np.nan))
+    assert "mask values" in both(mask=poke(b.mask, 7, 3))
+    # a bad mask value early and a non-finite log-probability later, and the other way round
+    assert "mask values" in both(mask=poke(b.mask, 2, 5), ref=poke(b.logp_ref, 9, np.inf))
+    assert "finite" in both(mask=poke(b.mask, 9, 5), ref=poke(b.logp_ref, 2, np.inf))
+    # advantages are looked at after every token, selected ids after the advantages
+    assert "advantages" in both(adv=poke(b.advantages, 1, np.nan), sel=poke(b.selected, active, b.V))
+    assert "vocabulary" in both(sel=poke(b.selected, active, -3))
+    assert "vocabulary" in both(sel=poke(b.selected, active, b.V), kernel=7)
+    assert "selector" in both(kernel=7)
+    # a response without a valid token is found last
+    empty = b.mask.copy()
+    empty[: b.T] = 0
+    assert "at least one valid token" in both(mask=empty)
+    assert "at least one valid token" not in both(mask=empty, old=poke(b.logp_old, 0, np.nan))
