@@ -59,6 +59,20 @@ def test_one_rank_matches_the_cpu_checker_and_the_reference_facing_call():
                 sel = b.selected.copy()
                 sel[int(np.flatnonzero(b.mask == 1)[0])] = b.V
                 shard.run(x, b.logp_old, b.logp_ref, sel, b.advantages, b.mask, cfg)
+            # several things wrong at once: the complaint that comes first in the reference's order
+            m2, r2 = b.mask.copy(), b.logp_ref.copy()
+            m2[2], r2[9] = 5, np.inf
+            with pytest.raises(RuntimeError, match="mask values must be 0 or 1"):
+                shard.run(x, b.logp_old, r2, b.selected, b.advantages, m2, cfg)
+            m2, r2 = b.mask.copy(), b.logp_ref.copy()
+            m2[9], r2[2] = 5, np.inf
+            with pytest.raises(RuntimeError, match="log probabilities must be finite"):
+                shard.run(x, b.logp_old, r2, b.selected, b.advantages, m2, cfg)
+            a2 = b.advantages.copy()
+            a2[1] = np.nan
+            with pytest.raises(RuntimeError, match="advantages must be finite"):
+                shard.run(x, b.logp_old, b.logp_ref, sel, a2, b.mask, cfg)
+            assert (x.cpu().numpy().view(np.uint32) == out.view(np.uint32)).all(), "rejected calls leave the logits alone"
             with pytest.raises(RuntimeError, match="logp_old has size 3, expected"):
                 shard.run(x, b.logp_old[:3], b.logp_ref, b.selected, b.advantages, b.mask, cfg)
             with pytest.raises(RuntimeError, match="logits_and_dlogits must not be null"):
