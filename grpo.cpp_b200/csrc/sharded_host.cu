@@ -8,8 +8,8 @@
 //
 // grpo_b200_logits_sharded_host is grpo_logits_cuda_device_inplace (src/cuda/grpo_loss_cuda.cu:774-817)
 // for one rank's rows of a batch: host metadata in, device logits replaced in place, the GLOBAL
-// loss terms out.  Per call: one packed pinned host-to-device copy, the lengths exchange, the row
-// order, the row kernel and the reduce kernel (with the record exchange) enqueued back to back
+// loss terms out.  Per call: one packed pinned host-to-device copy, the row order, the lengths
+// exchange, the row kernel and the reduce kernel (with the record exchange) enqueued back to back
 // without an intermediate synchronisation, one pinned read-back, and the reference's error
 // contract applied to the global quantities.
 #include <cmath>
@@ -250,13 +250,14 @@ int grpo_b200_logits_sharded_host(grpo_b200_shard_t s, float* logits_and_dlogits
 
     auto* rb_d = reinterpret_cast<Readback*>(s->readback_d);
     grpo_b200_stream_t st = reinterpret_cast<grpo_b200_stream_t>(s->stream);
-    // global lengths -> weights (exchange 1), row order, row kernel + reduce kernel with the record exchange
-    // (exchange 2; it also recounts the same mask for a next pass, which costs nothing and keeps one kernel)
+    // row order (local work first: the ranks reach the exchange a little closer together), global lengths ->
+    // weights (exchange 1), row kernel + reduce kernel with the record exchange (exchange 2; it also recounts
+    // the same mask for a next pass, which costs nothing and keeps one kernel)
+    if (int rc = grpo_b200_row_order(s->mask_d, s->n_rows, s->order_d, st)) return rc;
     if (int rc = grpo_b200_lengths_sharded(s->mask_d, s->n_rows, s->row_offset, s->tokens_per_seq, s->n_seq, s->regions,
                                            s->rank, s->world, reduction, length_alpha, s->weights_d, rb_d->meta, nullptr,
                                            &rb_d->lengths_status, s->work_d, s->work_bytes, st))
         return rc;
-    if (int rc = grpo_b200_row_order(s->mask_d, s->n_rows, s->order_d, st)) return rc;
     if (int rc = grpo_b200_logits_sharded(logits_and_dlogits, logits_and_dlogits, s->old_d, s->ref_d, s->sel_d, s->adv_d,
                                           s->weights_d, s->mask_d, s->n_rows, s->row_offset, s->tokens_per_seq, s->V, s->P,
                                           clip_eps, beta, kernel, 0, nullptr, s->order_d, &rb_d->record, s->work_d,

@@ -390,7 +390,7 @@ int grpo_b200_benchmark_logits_host(const float* logits, size_t n_logits, const 
  * grpo_b200_logits_sharded_host: this rank's host metadata in (logp_old, logp_ref, selected, mask:
  * n_rows entries each; advantages: all n_seq), this rank's device logits (n_rows x P) replaced in place
  * by dL/dlogits, and the GLOBAL loss, pg_loss, kl and valid-token count out -- the same on every rank,
- * bit for bit.  One packed pinned upload, the lengths exchange, the row order, the row kernel and the
+ * bit for bit.  One packed pinned upload, the row order, the lengths exchange, the row kernel and the
  * reduce kernel (with the record exchange over NVLink peer memory) enqueued on the legacy default stream
  * without an intermediate synchronisation, one pinned read-back; returns after the device work is
  * complete.  Errors as the reference's call, applied to the global quantities ("every sequence needs at
